@@ -1,0 +1,174 @@
+"""`approx_ops` - the compiled-operator module the reference Python layer imports by absolute name
+(`import approx_ops`, self_ops/ops_py/approx_ops.py:3), re-implemented on liblutgemm_b200.so.
+
+It exposes the three functions the reference registers in self_ops/src/op_register.cpp:16-19 with
+the same positional signatures, in-place outputs and precondition checks
+(self_ops/src/cuda_helper.h:64-74, approx_gemm_forward.cu:243-259, approx_gemm_backward.cu:508-529):
+
+    approx_gemm_forward (a: u8[M,K], b: u8[K,N], c: u32[M,N] (out), lut: u16[LUT_ELEM_NUM])
+    approx_gemm_backward(gc: f32[M,N], a, b, ga: f32[M,K] (out), gb: f32[K,N] (out),
+                         lut_ga: i16[LUT_ELEM_NUM], lut_gb: i16[LUT_ELEM_NUM])
+    acc_gemm_forward_fp32(a: f32[M,K], b: f32[K,N], c: f32[M,N] (out))
+
+Differences from the reference, all on the safe side: the bit-width is inferred from the table
+length instead of a compile-time macro; kernels run on the current PyTorch stream instead of the
+legacy default stream; a failed launch raises RuntimeError instead of printing and carrying on.
+There is no CPU or PyTorch fallback: without the CUDA library every call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "liblutgemm_b200.so")
+_lib = None
+
+
+def _load():
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(_LIB_PATH):
+        raise RuntimeError(
+            f"{_LIB_PATH} is missing: build it with `python {os.path.join(_HERE, 'build_ext.py')}` "
+            "(there is no fallback path for the LUT-GEMM operators)")
+    lib = ctypes.CDLL(_LIB_PATH)
+    vp, ci, cl, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_size_t
+    lib.lutgemm_version.restype = ci
+    lib.lutgemm_status_string.restype = ctypes.c_char_p
+    lib.lutgemm_status_string.argtypes = [ci]
+    lib.lutgemm_lut_elem_num.restype = ci
+    lib.lutgemm_lut_elem_num.argtypes = [ci]
+    lib.lutgemm_bits_from_elem_num.restype = ci
+    lib.lutgemm_bits_from_elem_num.argtypes = [cl]
+    lib.lutgemm_forward.restype = ci
+    lib.lutgemm_forward.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, vp]
+    lib.lutgemm_backward_scratch_bytes.restype = sz
+    lib.lutgemm_backward_scratch_bytes.argtypes = [ci, ci, ci, ci]
+    lib.lutgemm_backward.restype = ci
+    lib.lutgemm_backward.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp, sz, vp]
+    _lib = lib
+    return lib
+
+
+def library():
+    """The loaded ctypes handle of liblutgemm_b200.so (raises if it has not been built)."""
+    return _load()
+
+
+def _check(status: int, what: str) -> None:
+    if status != 0:
+        msg = _load().lutgemm_status_string(status).decode()
+        raise RuntimeError(f"{what} failed with status {status}: {msg}")
+
+
+def _check_input(x: torch.Tensor, dtype: torch.dtype, name: str) -> None:
+    if not isinstance(x, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if not x.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDAtensor")
+    if not x.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    if x.dtype != dtype:
+        raise RuntimeError(f"{name} must be of type {dtype}")
+
+
+def _bits_of(lut: torch.Tensor, name: str) -> int:
+    bits = _load().lutgemm_bits_from_elem_num(lut.numel())
+    if lut.dim() != 1 or bits < 0:
+        raise RuntimeError(f"{name} size should be one of 1024/5120/17408/66306 (4/6/7/8-bit tables), got "
+                           f"{tuple(lut.shape)}; please check the quantization bit-width")
+    return bits
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def approx_gemm_forward(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, lut: torch.Tensor) -> None:
+    """c[m,n] = sum_k lut[a[m,k]*(2^bits+2) + b[k,n]], written in place into the uint32 tensor c."""
+    _check_input(a, torch.uint8, "a_tensor")
+    _check_input(b, torch.uint8, "b_tensor")
+    _check_input(c, torch.uint32, "c_tensor")
+    _check_input(lut, torch.uint16, "lut_appmult_tensor")
+    if a.dim() != 2 or b.dim() != 2 or c.dim() != 2:
+        raise RuntimeError("a_tensor, b_tensor and c_tensor must be 2-D")
+    M, K = a.shape
+    N = b.shape[1]
+    if b.shape[0] != K:
+        raise RuntimeError(f"b_tensor's shape should be {K} x {N}")
+    if tuple(c.shape) != (M, N):
+        raise RuntimeError(f"c_tensor's shape should be {M} x {N}")
+    bits = _bits_of(lut, "lut_appmult_tensor")
+    dev = a.device
+    if b.device != dev or c.device != dev or lut.device != dev:
+        raise RuntimeError("device id not match")
+    if M == 0 or N == 0:
+        return
+    if K == 0:
+        c.zero_()
+        return
+    with torch.cuda.device(dev):
+        rc = _load().lutgemm_forward(a.data_ptr(), b.data_ptr(), c.data_ptr(), lut.data_ptr(), bits, M, K, N,
+                                     _stream_ptr(dev))
+    _check(rc, "approx_gemm_forward")
+
+
+def approx_gemm_backward(gc: torch.Tensor, a: torch.Tensor, b: torch.Tensor, ga: torch.Tensor, gb: torch.Tensor,
+                         lut_grad_a: torch.Tensor, lut_grad_b: torch.Tensor) -> None:
+    """ga = 1/16 * sum_n gc * LUTa[a][b],  gb = 1/16 * sum_m LUTb[a][b] * gc, written in place."""
+    _check_input(gc, torch.float32, "gc_tensor")
+    _check_input(a, torch.uint8, "a_tensor")
+    _check_input(b, torch.uint8, "b_tensor")
+    _check_input(ga, torch.float32, "ga_tensor")
+    _check_input(gb, torch.float32, "gb_tensor")
+    _check_input(lut_grad_a, torch.int16, "lut_grad_a_tensor")
+    _check_input(lut_grad_b, torch.int16, "lut_grad_b_tensor")
+    if a.dim() != 2 or b.dim() != 2:
+        raise RuntimeError("a_tensor and b_tensor must be 2-D")
+    M, K = a.shape
+    N = b.shape[1]
+    if tuple(gc.shape) != (M, N):
+        raise RuntimeError(f"gc_tensor's shape should be {M} x {N}")
+    if b.shape[0] != K:
+        raise RuntimeError(f"b_tensor's shape should be {K} x {N}")
+    if tuple(ga.shape) != (M, K):
+        raise RuntimeError(f"ga_tensor's shape should be {M} x {K}")
+    if tuple(gb.shape) != (K, N):
+        raise RuntimeError(f"gb_tensor's shape should be {K} x {N}")
+    bits = _bits_of(lut_grad_a, "lut_grad_a_tensor")
+    if _bits_of(lut_grad_b, "lut_grad_b_tensor") != bits:
+        raise RuntimeError("lut_grad_a_tensor and lut_grad_b_tensor must have the same length")
+    dev = gc.device
+    for t in (a, b, ga, gb, lut_grad_a, lut_grad_b):
+        if t.device != dev:
+            raise RuntimeError("All tensors should be on the same device")
+    if M == 0 or K == 0 or N == 0:
+        ga.zero_()
+        gb.zero_()
+        return
+    lib = _load()
+    with torch.cuda.device(dev):
+        nbytes = lib.lutgemm_backward_scratch_bytes(bits, M, K, N)
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev) if nbytes else None
+        rc = lib.lutgemm_backward(gc.data_ptr(), a.data_ptr(), b.data_ptr(), ga.data_ptr(), gb.data_ptr(),
+                                  lut_grad_a.data_ptr(), lut_grad_b.data_ptr(), bits, M, K, N,
+                                  scratch.data_ptr() if scratch is not None else None, nbytes, _stream_ptr(dev))
+    _check(rc, "approx_gemm_backward")
+
+
+def acc_gemm_forward_fp32(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor) -> None:
+    """Exact fp32 GEMM c = a @ b written in place.  The reference carries a hand-written SGEMM for this
+    (approx_gemm_forward.cu:340-571) that only its unused AccGemm wrapper calls; the symbol is kept
+    for API parity and forwards to the library GEMM."""
+    _check_input(a, torch.float32, "a_tensor")
+    _check_input(b, torch.float32, "b_tensor")
+    _check_input(c, torch.float32, "c_tensor")
+    if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[0]:
+        raise RuntimeError(f"b_tensor's shape should be {a.shape[1]} x N")
+    if tuple(c.shape) != (a.shape[0], b.shape[1]):
+        raise RuntimeError(f"c_tensor's shape should be {a.shape[0]} x {b.shape[1]}")
+    torch.mm(a, b, out=c)

@@ -1,0 +1,419 @@
+// Backward LUT-GEMM for sm_100a (gradient-table gathers fused with the grad_out multiply, fp32).
+//
+//   gA[m,k] = 1/16 * sum_n gC[m,n] * float(LUTa[a[m,k]][w[k,n]])      (ga_colbcast_kernel)
+//   gW[k,n] = 1/16 * sum_m float(LUTw[a[m,k]][w[k,n]]) * gC[m,n]      (gw_rowbcast_kernel)
+//
+// Both kernels keep the whole int16 gradient table in shared memory and make ONE of the two table
+// indices warp-uniform so a gather stays inside a single table row:
+//   gA: a thread owns gA[m, k..k+R) for C rows m; a[m,k] is fixed per thread, the weight code
+//       w[k,n] is the same for all lanes (they share the k set), and the table is staged TRANSPOSED
+//       ([w][a]) so the uniform index selects the row.  n ascends exactly as in the reference, so
+//       the fp32 sum order per element is the reference's.
+//   gW: a thread owns gW[k..k+R, n..n+C); w[k,n] is fixed per thread, the activation code a[m,k] is
+//       warp-uniform, table staged as [a][w].  The reduction over M (262144 rows for the CIFAR
+//       convolutions, against a 576x64 output) is split into slabs across CTAs; partial sums go to a
+//       scratch buffer and a second kernel adds the slabs in ascending order (deterministic).
+// Replaces ApproxGemmBackwardKernelForGA / ForGB, self_ops/src/approx_gemm_backward.cu:13-258,261-492.
+#include "lutgemm_common.cuh"
+#include "lutgemm_kernels.h"
+
+namespace lutgemm {
+
+// ------------------------------------------------------------------------------------------------
+// gA
+// ------------------------------------------------------------------------------------------------
+template <int BITS, int R, int C, int WM, int WK>
+struct GaCfg {
+    static constexpr int Q = 1 << BITS;
+    static constexpr int THREADS = 32 * WM * WK;
+    static constexpr int MT = WM * 32 * C;
+    static constexpr int KT = WK * R;
+    static constexpr int NT = 16;
+    static constexpr int GSTRIDE = NT * 4 + 16;  // bytes; odd multiple of 16 -> conflict-free 128-bit row reads
+    static constexpr int LUT_BYTES = Q * Q * 2;
+    static constexpr int G_STAGE = MT * GSTRIDE;
+    static constexpr int W_STAGE = KT * NT;
+    static constexpr int SMEM = LUT_BYTES + 2 * (G_STAGE + W_STAGE);
+};
+
+template <int BITS, int R, int C, int WM, int WK>
+__global__ void __launch_bounds__(32 * WM * WK, 1)
+ga_colbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, const uint8_t *__restrict__ w,
+                   float *__restrict__ ga, const int16_t *__restrict__ lut, int M, int K, int N, int tiles_m,
+                   int tiles_k, int vec_g, int vec_w, int vec_o) {
+    using Cfg = GaCfg<BITS, R, C, WM, WK>;
+    constexpr int MT = Cfg::MT, KT = Cfg::KT, NT = Cfg::NT, GS = Cfg::GSTRIDE, THREADS = Cfg::THREADS;
+    constexpr uint32_t MASK = Cfg::Q - 1;
+    static_assert(R % 4 == 0, "R k-columns per thread");
+
+    extern __shared__ __align__(16) uint8_t smem[];
+    int16_t *lut_s = reinterpret_cast<int16_t *>(smem);
+    uint8_t *g_s = smem + Cfg::LUT_BYTES;
+    uint8_t *w_s = g_s + 2 * Cfg::G_STAGE;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = warp / WK, wk = warp % WK;
+
+    stage_table<BITS, true>(lut_s, lut, tid, THREADS);
+    const uint32_t lut_addr = smem_u32(lut_s);
+    const int nnt = (N + NT - 1) / NT;
+
+    auto load_tile = [&](int m0, int k0, int nt, int buf) {
+        uint8_t *gs = g_s + buf * Cfg::G_STAGE;
+        uint8_t *ws = w_s + buf * Cfg::W_STAGE;
+        const int nbase = nt * NT;
+        if (vec_g) {
+            for (int id = tid; id < MT * (NT / 4); id += THREADS) {
+                int r = id / (NT / 4), nc = (id % (NT / 4)) * 4;
+                int gm = m0 + r, gn = nbase + nc;
+                if (gm < M && gn < N) cp_async16(gs + r * GS + nc * 4, gc + (size_t)gm * N + gn);
+                else *reinterpret_cast<float4 *>(gs + r * GS + nc * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        } else {
+            for (int id = tid; id < MT * NT; id += THREADS) {
+                int r = id / NT, nn = id % NT;
+                int gm = m0 + r, gn = nbase + nn;
+                *reinterpret_cast<float *>(gs + r * GS + nn * 4) = (gm < M && gn < N) ? gc[(size_t)gm * N + gn] : 0.f;
+            }
+        }
+        if (vec_w) {
+            for (int id = tid; id < KT; id += THREADS) {
+                int gk = k0 + id;
+                if (gk < K && nbase < N) cp_async16(ws + id * NT, w + (size_t)gk * N + nbase);
+                else *reinterpret_cast<uint4 *>(ws + id * NT) = make_uint4(0, 0, 0, 0);
+            }
+        } else {
+            for (int id = tid; id < KT * NT; id += THREADS) {
+                int kk = id / NT, nn = id % NT;
+                int gk = k0 + kk, gn = nbase + nn;
+                ws[id] = (gk < K && gn < N) ? w[(size_t)gk * N + gn] : (uint8_t)0;
+            }
+        }
+        cp_async_commit();
+    };
+
+    for (int tile = blockIdx.x; tile < tiles_m * tiles_k; tile += gridDim.x) {
+        const int m0 = (tile / tiles_k) * MT, k0 = (tile % tiles_k) * KT;
+        const int kth = k0 + wk * R;           // first k of this thread
+        const int mth = m0 + wm * 32 * C + lane;  // first m of this thread; rows mth + 32*j
+
+        uint32_t aoff[R][C];
+        float acc[R][C];
+#pragma unroll
+        for (int j = 0; j < C; ++j) {
+            const int m = mth + 32 * j;
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
+                const int k = kth + i;
+                uint32_t code = (m < M && k < K) ? a[(size_t)m * K + k] : 0u;
+                aoff[i][j] = (code & MASK) * 2u;
+                acc[i][j] = 0.f;
+            }
+        }
+
+        load_tile(m0, k0, 0, 0);
+        for (int nt = 0; nt < nnt; ++nt) {
+            cp_async_wait<0>();
+            __syncthreads();
+            if (nt + 1 < nnt) load_tile(m0, k0, nt + 1, (nt + 1) & 1);
+            const uint8_t *gs = g_s + (nt & 1) * Cfg::G_STAGE + (wm * 32 * C + lane) * GS;
+            const uint8_t *ws = w_s + (nt & 1) * Cfg::W_STAGE + (wk * R) * NT;
+#pragma unroll 1
+            for (int n4 = 0; n4 < NT; n4 += 4) {
+                uint32_t w4[R];
+                float4 g4[C];
+#pragma unroll
+                for (int i = 0; i < R; ++i) w4[i] = *reinterpret_cast<const uint32_t *>(ws + i * NT + n4);
+#pragma unroll
+                for (int j = 0; j < C; ++j) g4[j] = *reinterpret_cast<const float4 *>(gs + (32 * j) * GS + n4 * 4);
+#pragma unroll
+                for (int nn = 0; nn < 4; ++nn) {
+#pragma unroll
+                    for (int i = 0; i < R; ++i) {
+                        const uint32_t wrow = lut_addr + ((byte_of(w4[i], nn) & MASK) << (BITS + 1));
+#pragma unroll
+                        for (int j = 0; j < C; ++j) {
+                            const float g = nn == 0 ? g4[j].x : nn == 1 ? g4[j].y : nn == 2 ? g4[j].z : g4[j].w;
+                            acc[i][j] = fmaf(g, (float)lds_s16(wrow + aoff[i][j]), acc[i][j]);
+                        }
+                    }
+                }
+            }
+        }
+
+#pragma unroll
+        for (int j = 0; j < C; ++j) {
+            const int m = mth + 32 * j;
+            if (m >= M) continue;
+            float *orow = ga + (size_t)m * K + kth;
+            if (vec_o) {
+#pragma unroll
+                for (int i = 0; i < R; i += 4)
+                    if (kth + i < K)
+                        *reinterpret_cast<float4 *>(orow + i) =
+                            make_float4(acc[i][j] * kGradFactor, acc[i + 1][j] * kGradFactor,
+                                        acc[i + 2][j] * kGradFactor, acc[i + 3][j] * kGradFactor);
+            } else {
+#pragma unroll
+                for (int i = 0; i < R; ++i)
+                    if (kth + i < K) orow[i] = acc[i][j] * kGradFactor;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+template <int BITS, int R, int C, int WM, int WK>
+static int launch_ga(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, const int16_t *lut, int M,
+                     int K, int N, int num_sms, cudaStream_t stream) {
+    using Cfg = GaCfg<BITS, R, C, WM, WK>;
+    auto kern = ga_colbcast_kernel<BITS, R, C, WM, WK>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess)
+        return LUTGEMM_E_CUDA;
+    const int tiles_m = (M + Cfg::MT - 1) / Cfg::MT, tiles_k = (K + Cfg::KT - 1) / Cfg::KT;
+    const long tiles = (long)tiles_m * tiles_k;
+    const int ctas_per_sm = Cfg::SMEM <= 100 * 1024 ? 2 : 1;
+    const int grid = (int)(tiles < (long)num_sms * ctas_per_sm ? tiles : (long)num_sms * ctas_per_sm);
+    const int vec_g = (N % 4 == 0) && ((reinterpret_cast<uintptr_t>(gc) & 15) == 0);
+    const int vec_w = (N % 16 == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
+    const int vec_o = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(ga) & 15) == 0);
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(gc, a, w, ga, lut, M, K, N, tiles_m, tiles_k, vec_g, vec_w, vec_o);
+    return cudaGetLastError() == cudaSuccess ? LUTGEMM_OK : LUTGEMM_E_CUDA;
+}
+
+int backward_ga(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, const int16_t *lut_ga, int bits,
+                int M, int K, int N, int num_sms, cudaStream_t stream) {
+    switch (bits) {
+        case 4: return launch_ga<4, 8, 4, 2, 4>(gc, a, w, ga, lut_ga, M, K, N, num_sms, stream);
+        case 6: return launch_ga<6, 8, 4, 2, 4>(gc, a, w, ga, lut_ga, M, K, N, num_sms, stream);
+        case 7: return launch_ga<7, 8, 4, 2, 4>(gc, a, w, ga, lut_ga, M, K, N, num_sms, stream);
+        case 8: return launch_ga<8, 8, 4, 2, 4>(gc, a, w, ga, lut_ga, M, K, N, num_sms, stream);
+    }
+    return LUTGEMM_E_BITS;
+}
+
+// ------------------------------------------------------------------------------------------------
+// gW
+// ------------------------------------------------------------------------------------------------
+template <int BITS, int R, int C, int WK, int WN>
+struct GwCfg {
+    static constexpr int Q = 1 << BITS;
+    static constexpr int THREADS = 32 * WK * WN;
+    static constexpr int KT = WK * R;
+    static constexpr int NT = WN * 32 * C;
+    static constexpr int MT = 16;
+    static constexpr int LUT_BYTES = Q * Q * 2;
+    static constexpr int A_STAGE = MT * KT;
+    static constexpr int G_STAGE = MT * NT * 4;
+    static constexpr int SMEM = LUT_BYTES + 2 * (A_STAGE + G_STAGE);
+};
+
+constexpr int kGwWideR = 4, kGwWideC = 8, kGwNarrowR = 16, kGwNarrowC = 2, kGwWarps = 8;
+constexpr int kGwMinRowsPerSplit = 512;
+
+template <int BITS, int R, int C, int WK, int WN>
+__global__ void __launch_bounds__(32 * WK * WN, 1)
+gw_rowbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, const uint8_t *__restrict__ w,
+                   float *__restrict__ out, const int16_t *__restrict__ lut, int M, int K, int N, int tiles_k,
+                   int tiles_n, int num_splits, int rows_per_split, float out_scale, int vec_a, int vec_g) {
+    using Cfg = GwCfg<BITS, R, C, WK, WN>;
+    constexpr int MT = Cfg::MT, KT = Cfg::KT, NT = Cfg::NT, THREADS = Cfg::THREADS;
+    constexpr uint32_t MASK = Cfg::Q - 1;
+    static_assert(R == 4 || R == 16, "R k-rows per thread");
+    static_assert(C == 2 || C == 8, "C columns per lane");
+
+    extern __shared__ __align__(16) uint8_t smem[];
+    int16_t *lut_s = reinterpret_cast<int16_t *>(smem);
+    uint8_t *a_s = smem + Cfg::LUT_BYTES;
+    uint8_t *g_s = a_s + 2 * Cfg::A_STAGE;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wk = warp / WN, wn = warp % WN;
+
+    stage_table<BITS, false>(lut_s, lut, tid, THREADS);
+    const uint32_t lut_addr = smem_u32(lut_s);
+
+    auto load_tile = [&](int k0, int n0, int mbase, int mend, int buf) {
+        uint8_t *as = a_s + buf * Cfg::A_STAGE;
+        float *gs = reinterpret_cast<float *>(g_s + buf * Cfg::G_STAGE);
+        if (vec_a) {
+            for (int id = tid; id < MT * (KT / 16); id += THREADS) {
+                int r = id / (KT / 16), kc = (id % (KT / 16)) * 16;
+                int gm = mbase + r, gk = k0 + kc;
+                if (gm < mend && gk < K) cp_async16(as + r * KT + kc, a + (size_t)gm * K + gk);
+                else *reinterpret_cast<uint4 *>(as + r * KT + kc) = make_uint4(0, 0, 0, 0);
+            }
+        } else {
+            for (int id = tid; id < MT * KT; id += THREADS) {
+                int r = id / KT, kk = id % KT;
+                int gm = mbase + r, gk = k0 + kk;
+                as[id] = (gm < mend && gk < K) ? a[(size_t)gm * K + gk] : (uint8_t)0;
+            }
+        }
+        if (vec_g) {
+            for (int id = tid; id < MT * (NT / 4); id += THREADS) {
+                int r = id / (NT / 4), nc = (id % (NT / 4)) * 4;
+                int gm = mbase + r, gn = n0 + nc;
+                if (gm < mend && gn < N) cp_async16(gs + r * NT + nc, gc + (size_t)gm * N + gn);
+                else *reinterpret_cast<float4 *>(gs + r * NT + nc) = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        } else {
+            for (int id = tid; id < MT * NT; id += THREADS) {
+                int r = id / NT, nn = id % NT;
+                int gm = mbase + r, gn = n0 + nn;
+                gs[id] = (gm < mend && gn < N) ? gc[(size_t)gm * N + gn] : 0.f;
+            }
+        }
+        cp_async_commit();
+    };
+
+    const long items = (long)tiles_k * tiles_n * num_splits;
+    for (long item = blockIdx.x; item < items; item += gridDim.x) {
+        const int split = (int)(item % num_splits);
+        const int tile = (int)(item / num_splits);
+        const int k0 = (tile / tiles_n) * KT, n0 = (tile % tiles_n) * NT;
+        const int mbeg = split * rows_per_split;
+        const int mend = min(M, mbeg + rows_per_split);
+        // column of accumulator j: lanes interleave in groups of 4 columns so that every 128-bit read
+        // of the grad_out tile is contiguous across the warp (C == 8), or plain pairs (C == 2)
+        auto col_of = [&](int j) { return C == 8 ? (j >> 2) * 128 + lane * 4 + (j & 3) : lane * C + j; };
+        const int kth = k0 + wk * R, nth = n0 + wn * 32 * C;
+
+        uint32_t woff[R][C];
+        float acc[R][C];
+#pragma unroll
+        for (int i = 0; i < R; ++i)
+#pragma unroll
+            for (int j = 0; j < C; ++j) {
+                const int k = kth + i, n = nth + col_of(j);
+                uint32_t code = (k < K && n < N) ? w[(size_t)k * N + n] : 0u;
+                woff[i][j] = (code & MASK) * 2u;
+                acc[i][j] = 0.f;
+            }
+
+        const int nmt = (mend - mbeg + MT - 1) / MT;
+        if (nmt > 0) load_tile(k0, n0, mbeg, mend, 0);
+        for (int mt = 0; mt < nmt; ++mt) {
+            cp_async_wait<0>();
+            __syncthreads();
+            if (mt + 1 < nmt) load_tile(k0, n0, mbeg + (mt + 1) * MT, mend, (mt + 1) & 1);
+            const uint8_t *as = a_s + (mt & 1) * Cfg::A_STAGE + wk * R;
+            const float *gs = reinterpret_cast<const float *>(g_s + (mt & 1) * Cfg::G_STAGE) + wn * 32 * C +
+                              (C == 8 ? lane * 4 : lane * C);
+#pragma unroll 2
+            for (int mm = 0; mm < MT; ++mm) {
+                uint32_t av[R / 4];
+                if constexpr (R == 4) {
+                    av[0] = *reinterpret_cast<const uint32_t *>(as + mm * KT);
+                } else {
+                    uint4 t = *reinterpret_cast<const uint4 *>(as + mm * KT);
+                    av[0] = t.x; av[1] = t.y; av[2] = t.z; av[3] = t.w;
+                }
+                float g[C];
+                if constexpr (C == 8) {
+                    float4 t0 = *reinterpret_cast<const float4 *>(gs + mm * NT);
+                    float4 t1 = *reinterpret_cast<const float4 *>(gs + mm * NT + 128);
+                    g[0] = t0.x; g[1] = t0.y; g[2] = t0.z; g[3] = t0.w;
+                    g[4] = t1.x; g[5] = t1.y; g[6] = t1.z; g[7] = t1.w;
+                } else {
+                    float2 t0 = *reinterpret_cast<const float2 *>(gs + mm * NT);
+                    g[0] = t0.x; g[1] = t0.y;
+                }
+#pragma unroll
+                for (int i = 0; i < R; ++i) {
+                    const uint32_t arow = lut_addr + ((byte_of(av[i / 4], i % 4) & MASK) << (BITS + 1));
+#pragma unroll
+                    for (int j = 0; j < C; ++j)
+                        acc[i][j] = fmaf((float)lds_s16(arow + woff[i][j]), g[j], acc[i][j]);
+                }
+            }
+        }
+
+        float *obase = out + (num_splits > 1 ? (size_t)split * K * N : (size_t)0);
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            const int k = kth + i;
+            if (k >= K) continue;
+#pragma unroll
+            for (int j = 0; j < C; ++j)
+                if (nth + col_of(j) < N) obase[(size_t)k * N + nth + col_of(j)] = acc[i][j] * out_scale;
+        }
+        __syncthreads();
+    }
+}
+
+__global__ void gw_reduce_splits_kernel(const float *__restrict__ partial, float *__restrict__ gw, long KN,
+                                        int num_splits, float scale) {
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < KN; i += (long)gridDim.x * blockDim.x) {
+        float s = 0.f;
+        for (int p = 0; p < num_splits; ++p) s += partial[(size_t)p * KN + i];
+        gw[i] = s * scale;
+    }
+}
+
+static bool gw_use_narrow(int N) { return N <= 128; }
+
+int gw_num_splits(int bits, int M, int K, int N, int num_sms) {
+    (void)bits;
+    const int kt = gw_use_narrow(N) ? kGwWarps * kGwNarrowR : kGwWarps * kGwWideR;
+    const int nt = gw_use_narrow(N) ? 32 * kGwNarrowC : 32 * kGwWideC;
+    const long tiles = (long)((K + kt - 1) / kt) * ((N + nt - 1) / nt);
+    long want = (2L * num_sms + tiles - 1) / tiles;
+    long cap = M / kGwMinRowsPerSplit;
+    if (want > cap) want = cap;
+    if (want < 1) want = 1;
+    if (want > 4096) want = 4096;
+    return (int)want;
+}
+
+template <int BITS, int R, int C, int WK, int WN>
+static int launch_gw(const float *gc, const uint8_t *a, const uint8_t *w, float *gw, const int16_t *lut, int M,
+                     int K, int N, float *scratch, int num_splits, int num_sms, cudaStream_t stream) {
+    using Cfg = GwCfg<BITS, R, C, WK, WN>;
+    auto kern = gw_rowbcast_kernel<BITS, R, C, WK, WN>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess)
+        return LUTGEMM_E_CUDA;
+    const int tiles_k = (K + Cfg::KT - 1) / Cfg::KT, tiles_n = (N + Cfg::NT - 1) / Cfg::NT;
+    const long items = (long)tiles_k * tiles_n * num_splits;
+    const int ctas_per_sm = Cfg::SMEM <= 100 * 1024 ? 2 : 1;
+    const int grid = (int)(items < (long)num_sms * ctas_per_sm ? items : (long)num_sms * ctas_per_sm);
+    int rows_per_split = (M + num_splits - 1) / num_splits;
+    rows_per_split = (rows_per_split + Cfg::MT - 1) / Cfg::MT * Cfg::MT;
+    const int vec_a = (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(a) & 15) == 0);
+    const int vec_g = (N % 4 == 0) && ((reinterpret_cast<uintptr_t>(gc) & 15) == 0);
+    float *out = num_splits > 1 ? scratch : gw;
+    const float scale = num_splits > 1 ? 1.0f : kGradFactor;
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(gc, a, w, out, lut, M, K, N, tiles_k, tiles_n, num_splits,
+                                                    rows_per_split, scale, vec_a, vec_g);
+    if (cudaGetLastError() != cudaSuccess) return LUTGEMM_E_CUDA;
+    if (num_splits > 1) {
+        const long KN = (long)K * N;
+        const int rgrid = (int)((KN + 255) / 256 < 4L * num_sms ? (KN + 255) / 256 : 4L * num_sms);
+        gw_reduce_splits_kernel<<<rgrid, 256, 0, stream>>>(scratch, gw, KN, num_splits, kGradFactor);
+        if (cudaGetLastError() != cudaSuccess) return LUTGEMM_E_CUDA;
+    }
+    return LUTGEMM_OK;
+}
+
+template <int BITS>
+static int dispatch_gw(const float *gc, const uint8_t *a, const uint8_t *w, float *gw, const int16_t *lut, int M,
+                       int K, int N, float *scratch, int num_splits, int num_sms, cudaStream_t stream) {
+    if (gw_use_narrow(N))
+        return launch_gw<BITS, kGwNarrowR, kGwNarrowC, kGwWarps, 1>(gc, a, w, gw, lut, M, K, N, scratch, num_splits,
+                                                                     num_sms, stream);
+    return launch_gw<BITS, kGwWideR, kGwWideC, kGwWarps, 1>(gc, a, w, gw, lut, M, K, N, scratch, num_splits, num_sms,
+                                                             stream);
+}
+
+int backward_gw(const float *gc, const uint8_t *a, const uint8_t *w, float *gw, const int16_t *lut_gw, int bits,
+                int M, int K, int N, float *scratch, int num_splits, int num_sms, cudaStream_t stream) {
+    switch (bits) {
+        case 4: return dispatch_gw<4>(gc, a, w, gw, lut_gw, M, K, N, scratch, num_splits, num_sms, stream);
+        case 6: return dispatch_gw<6>(gc, a, w, gw, lut_gw, M, K, N, scratch, num_splits, num_sms, stream);
+        case 7: return dispatch_gw<7>(gc, a, w, gw, lut_gw, M, K, N, scratch, num_splits, num_sms, stream);
+        case 8: return dispatch_gw<8>(gc, a, w, gw, lut_gw, M, K, N, scratch, num_splits, num_sms, stream);
+    }
+    return LUTGEMM_E_BITS;
+}
+
+}  // namespace lutgemm

@@ -1,0 +1,86 @@
+// Shared device/host helpers of the sm_100a LUT-GEMM kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "lutgemm.h"
+
+namespace lutgemm {
+
+// ---- table geometry of the wire format (reference: self_ops/src/approx_mult.h:12-41) -------------
+__host__ __device__ constexpr int lut_col_num(int bits) { return (1 << bits) + 2; }
+__host__ __device__ constexpr int lut_row_num(int bits) { return (1 << bits) + 1; }
+__host__ __device__ constexpr int lut_tail_pad(int bits) {
+    return bits == 4 ? 718 : bits == 6 ? 830 : bits == 7 ? 638 : 0;
+}
+__host__ __device__ constexpr int lut_elem_num(int bits) {
+    return lut_row_num(bits) * lut_col_num(bits) + lut_tail_pad(bits);
+}
+constexpr float kGradFactor = 1.0f / 16.0f;  // approx_mult.h:41
+
+inline bool bits_supported(int bits) { return bits == 4 || bits == 6 || bits == 7 || bits == 8; }
+
+// ---- small device helpers ----------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+// 16-bit shared-memory gathers that land zero-/sign-extended in a 32-bit register (no cvt needed)
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    uint32_t v;
+    asm("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ int32_t lds_s16(uint32_t addr) {
+    int32_t v;
+    asm("ld.shared.s16 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ uint32_t byte_of(uint32_t v, int i) { return (v >> (8 * i)) & 0xffu; }
+
+// Stage the padded wire-format table into shared memory as a dense [2^BITS][2^BITS] array of 16-bit
+// entries.  TRANSPOSE=false: dst[a][w]; TRANSPOSE=true: dst[w][a].  The reference copies the padded
+// table verbatim once per output tile (approx_gemm_forward.cu:81-92); here a persistent CTA stages
+// it once per launch into the layout its gather pattern wants.
+template <int BITS, bool TRANSPOSE, typename T>
+__device__ __forceinline__ void stage_table(T *dst, const T *__restrict__ src, int tid, int nthreads) {
+    constexpr int Q = 1 << BITS;
+    constexpr int COL = lut_col_num(BITS);
+    if (!TRANSPOSE) {
+        if ((reinterpret_cast<uintptr_t>(src) & 3u) == 0) {
+            // rows start at a*COL (COL even) so pairs of entries are 4-byte aligned
+            const uint32_t *s32 = reinterpret_cast<const uint32_t *>(src);
+            uint32_t *d32 = reinterpret_cast<uint32_t *>(dst);
+            for (int i = tid; i < Q * Q / 2; i += nthreads) {
+                int a = i / (Q / 2), wp = i % (Q / 2);
+                d32[i] = __ldg(s32 + a * (COL / 2) + wp);
+            }
+        } else {
+            for (int i = tid; i < Q * Q; i += nthreads) dst[i] = src[(i >> BITS) * COL + (i & (Q - 1))];
+        }
+    } else {
+        // consecutive threads take consecutive a (contiguous shared-memory writes, strided L2 reads)
+        for (int i = tid; i < Q * Q; i += nthreads) {
+            int w = i >> BITS, a = i & (Q - 1);
+            dst[i] = src[a * COL + w];
+        }
+    }
+}
+
+}  // namespace lutgemm

@@ -1,0 +1,85 @@
+/*
+ * lutgemm.h - C ABI of the sm_100a approximate-multiplier LUT-GEMM library (liblutgemm_b200.so).
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle (cudaStream_t passed
+ * as void*; NULL = the legacy default stream).  All functions return 0 on success and a negative
+ * LUTGEMM_E_* status otherwise; nothing here prints, exits or throws.  The library keeps no mutable
+ * host state apart from idempotent per-device attribute caches, so calls are re-entrant across
+ * host threads.  Each entry point names the reference interface it replaces (paths are relative to
+ * the reference project changmg/AppMult-Aware-Retraining).
+ *
+ * Table wire format (self_ops/src/approx_mult.h:12-41, self_ops/ops_py/approx_ops.py:18-79):
+ * a flat array of LUT_ELEM_NUM entries, entry (a, w) at a*(2^bits+2) + w, everything outside
+ * [0,2^bits)^2 zero.  LUT_ELEM_NUM is 1024 / 5120 / 17408 / 66306 for bits = 4 / 6 / 7 / 8.
+ * Operand codes must lie in [0, 2^bits); the kernels mask codes to `bits` bits so a stray code can
+ * never read outside the staged table.
+ */
+#ifndef LUTGEMM_H
+#define LUTGEMM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LUTGEMM_OK 0
+#define LUTGEMM_E_BADARG (-1)      /* null pointer, non-positive size, misaligned buffer */
+#define LUTGEMM_E_BITS (-2)        /* bits not in {4,6,7,8} */
+#define LUTGEMM_E_CUDA (-3)        /* a CUDA runtime call or the kernel launch failed */
+#define LUTGEMM_E_SCRATCH (-4)     /* scratch buffer too small */
+#define LUTGEMM_E_TOOLARGE (-5)    /* size beyond what the entry point supports */
+
+/* Library version (major*10000 + minor*100 + patch). */
+int lutgemm_version(void);
+
+/* Human-readable text for a status code; for LUTGEMM_E_CUDA the last CUDA error string of the
+ * calling thread is appended.  The returned pointer is valid until the thread's next call. */
+const char *lutgemm_status_string(int status);
+
+/* Padded flat table length for a bit-width, or LUTGEMM_E_BITS.
+ * Replaces the compile-time LUT_ELEM_NUM of self_ops/src/approx_mult.h:12-38. */
+int lutgemm_lut_elem_num(int bits);
+
+/* Inverse of the above: bit-width whose padded table has `elem_num` entries, or LUTGEMM_E_BITS.
+ * The reference fixes the bit-width at compile time (approx_mult.h:12); here it is inferred from
+ * the table the caller passes, so one binary serves every width. */
+int lutgemm_bits_from_elem_num(long elem_num);
+
+/*
+ * Forward:  c[m,n] = sum_{k<K} lut[a[m,k]*(2^bits+2) + w[k,n]]      (uint32 accumulate, exact)
+ *   a   [M,K] uint8 row-major      w [K,N] uint8 row-major      c [M,N] uint32 row-major (overwritten)
+ *   lut flat uint16 [lutgemm_lut_elem_num(bits)]
+ * Replaces approx_gemm_forward_gpu, self_ops/src/approx_gemm_forward.cu:241-314 (kernel :37-229),
+ * bound to Python at self_ops/src/op_register.cpp:16.
+ */
+int lutgemm_forward(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits,
+                    int M, int K, int N, void *stream);
+
+/*
+ * Scratch bytes lutgemm_backward needs for a problem (0 when none is needed).  The weight-gradient
+ * kernel splits its long reduction over M into slabs whose partial sums live in this buffer.
+ * No counterpart in the reference (its GB kernel never splits M, approx_gemm_backward.cu:587-608).
+ */
+size_t lutgemm_backward_scratch_bytes(int bits, int M, int K, int N);
+
+/*
+ * Backward:  ga[m,k] = (1/16) * sum_{n<N} gc[m,n] * float(lut_ga[a[m,k]*(2^bits+2) + w[k,n]])
+ *            gw[k,n] = (1/16) * sum_{m<M} float(lut_gw[a[m,k]*(2^bits+2) + w[k,n]]) * gc[m,n]
+ *   gc [M,N] float32    ga [M,K] float32 (overwritten)    gw [K,N] float32 (overwritten)
+ *   lut_ga, lut_gw flat int16 tables holding round(16 * dAM/da) and round(16 * dAM/dw)
+ *   ga or gw may be NULL to skip that gradient.
+ *   scratch: device buffer of at least lutgemm_backward_scratch_bytes() bytes (may be NULL when
+ *   that is 0); its contents on return are unspecified.
+ * Replaces approx_gemm_backward_gpu, self_ops/src/approx_gemm_backward.cu:506-624 (kernels :13-258
+ * and :261-492), bound to Python at self_ops/src/op_register.cpp:18.
+ */
+int lutgemm_backward(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, float *gw,
+                     const int16_t *lut_ga, const int16_t *lut_gw, int bits, int M, int K, int N,
+                     void *scratch, size_t scratch_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LUTGEMM_H */
