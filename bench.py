@@ -1,0 +1,392 @@
+#!/usr/bin/env python
+"""Benchmark of the LUT-GEMM hot path (forward + both gradient-table gathers).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--bits 8] [--size 4096]
+
+One "step" is one forward plus one backward (gW then gA) LUT-GEMM over a batch of synthetic codes:
+M = K = N = --size (default 4096) at --bits (default 8), tables built like the benchmark's synthetic
+multiplier (max(0, x*y + e), window-difference gradients, wire format uint16 / int16 x16).
+Work unit: one LUT-MAC = one (m,k,n) gather-and-accumulate; a step is 3*M*K*N of them.
+With N > 1 ranks (torchrun) every rank runs its own M-shard of the same size (weak scaling over the
+batch dimension) and the weight gradient is summed across ranks with one NCCL all-reduce per step.
+Rank 0 prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.join(ROOT, "appmult-aware-retraining_b200")
+for p in (ROOT, PKG):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import numpy as np  # noqa: E402
+
+L2_BYTES = 126 * 1024 * 1024
+LSU_LOOKUPS_PER_CLK_PER_SM = 32
+
+
+# ------------------------------------------------------------------------------------------------
+# synthetic tables / inputs (definition shared with the tests through the benchmark's own formulae)
+# ------------------------------------------------------------------------------------------------
+def synthetic_wire_tables(bits: int, seed: int = 0):
+    """L[x][y] = max(0, x*y + e), e ~ U{-2^(b-1)..2^(b-1)}; gradients = clipped window difference with
+    half window 2^b/16; returned in the wire format (uint16, int16 = round(16*g)) as dense arrays."""
+    q = 1 << bits
+    h = max(1, q // 16)
+    rng = np.random.default_rng(seed)
+    e = rng.integers(-(q // 2), q // 2 + 1, size=(q, q))
+    x = np.arange(q)
+    L = np.maximum(0, x[:, None] * x[None, :] + e).astype(np.int64)
+    hi, lo = np.minimum(x + h, q - 1), np.maximum(x - h, 0)
+    ga = (L[hi, :] - L[lo, :]) / (hi - lo)[:, None]
+    gb = (L[:, hi] - L[:, lo]) / (hi - lo)[None, :]
+    return L, np.round(ga * 16).astype(np.int64), np.round(gb * 16).astype(np.int64)
+
+
+def pack_wire(dense, bits, dtype):
+    q = 1 << bits
+    row, col = q + 1, q + 2
+    pad = {4: 718, 6: 830, 7: 638, 8: 0}[bits]
+    flat = np.zeros(row * col + pad, dtype)
+    flat[: row * col].reshape(row, col)[:q, :q] = dense
+    return flat
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=self.out, stderr=subprocess.DEVNULL)
+        except (OSError, FileNotFoundError):
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.out.close()
+        sm, smmax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1])); smmax.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for nm, v in zip(names, parts[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(nm)
+        os.unlink(self.path)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(smmax)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "sm_max_mhz": 1965.0}, "fallback"
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm / cpu baseline: the oracle port on the host cores
+# ------------------------------------------------------------------------------------------------
+def cpu_port_rate(bits, K, N, lf, la, lw, w, target_seconds=12.0, rows_cap=4096, seed=0):
+    """G LUT-MAC/s of the C/OpenMP oracle port for forward + backward on a bounded row sample of the
+    same problem (same K, N and weight codes; `rows` activation rows)."""
+    from oracle import OracleC
+    oc = OracleC()
+    rng = np.random.default_rng(seed)
+    q = 1 << bits
+
+    def run(rows):
+        a = rng.integers(0, q, (rows, K)).astype(np.uint8)
+        gc = rng.standard_normal((rows, N)).astype(np.float32)
+        t0 = time.perf_counter()
+        oc.forward(a, w, lf, bits)
+        oc.backward(gc, a, w, la, lw, bits)
+        return time.perf_counter() - t0
+
+    probe_rows = 16
+    t_probe = run(probe_rows)
+    rows = int(min(rows_cap, max(probe_rows, probe_rows * target_seconds / max(t_probe, 1e-6))))
+    t = run(rows)
+    return 3.0 * rows * K * N / t / 1e9, oc.num_threads(), rows, t
+
+
+def run_reference_arm(args, rank, world):
+    if rank != 0:
+        return
+    bits, S = args.bits, args.size
+    L, qa, qb = synthetic_wire_tables(bits, 0)
+    lf, la, lw = pack_wire(L, bits, np.uint16), pack_wire(qa, bits, np.int16), pack_wire(qb, bits, np.int16)
+    rng = np.random.default_rng(1)
+    w = rng.integers(0, 1 << bits, (S, S)).astype(np.uint8)
+    per_step_seconds = max(2.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
+    rates, rows, cores, tsum = [], 0, 1, 0.0
+    for i in range(args.warmup + args.steps):
+        r, cores, rows, t = cpu_port_rate(bits, S, S, lf, la, lw, w, target_seconds=per_step_seconds, rows_cap=S, seed=i)
+        if i >= args.warmup:
+            rates.append(r); tsum += t
+    value = float(np.mean(rates))
+    line = {
+        "impl": "reference", "metric": "lut_gemm_fwd_bwd_throughput", "value": value, "unit": "G LUT-MAC/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * tsum / max(1, args.steps),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u16 table -> u32 / f32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": f"lutgemm fwd+bwd {bits}-bit M=K=N={S}", "bits": bits, "M": S, "K": S, "N": S},
+        "cpu_baseline": {"value": value, "unit": "G LUT-MAC/s", "cores": cores, "kind": "port",
+                         "sample": f"{rows} of {S} activation rows per step, full K and N, fwd+bwd (C/OpenMP port of "
+                                   "the reference gather semantics; the reference has no CPU implementation)"},
+        "e2e": {"value": value, "unit": "G LUT-MAC/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+
+    import approx_ops
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device for --impl ours (there is no CPU fallback)")
+    lib = approx_ops.library()
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    bits, S = args.bits, args.size
+    M = K = N = S
+    L, qa, qb = synthetic_wire_tables(bits, 0)
+    lf = torch.from_numpy(pack_wire(L, bits, np.uint16)).to(dev)
+    la = torch.from_numpy(pack_wire(qa, bits, np.int16)).to(dev)
+    lw = torch.from_numpy(pack_wire(qb, bits, np.int16)).to(dev)
+
+    # Two rotating input/output sets: a step touches ~3x the L2 capacity, and consecutive steps use
+    # different buffers, so no operand of a step is L2-resident from the step before.
+    nsets = 2
+    g = torch.Generator(device="cpu").manual_seed(1000 + rank)
+    w_host = torch.from_numpy(np.random.default_rng(1).integers(0, 1 << bits, (K, N)).astype(np.uint8))
+    sets = []
+    for s in range(nsets):
+        a_h = torch.randint(0, 1 << bits, (M, K), generator=g, dtype=torch.uint8).pin_memory()
+        gc_h = torch.randn(M, N, generator=g).pin_memory()
+        sets.append({
+            "a_h": a_h, "gc_h": gc_h, "w_h": w_host.clone().pin_memory(),
+            "a": a_h.to(dev), "w": w_host.to(dev), "gc": gc_h.to(dev),
+            "c": torch.empty(M, N, dtype=torch.uint32, device=dev),
+            "ga": torch.empty(M, K, dtype=torch.float32, device=dev),
+            "gw": torch.empty(K, N, dtype=torch.float32, device=dev),
+        })
+    scratch_bytes = lib.lutgemm_backward_scratch_bytes(bits, M, K, N)
+    scratch = torch.empty(max(1, scratch_bytes), dtype=torch.uint8, device=dev)
+    launches_per_step = 3 + (1 if scratch_bytes else 0)
+    stream = torch.cuda.current_stream(dev)
+
+    def fwd(s):
+        rc = lib.lutgemm_forward(s["a"].data_ptr(), s["w"].data_ptr(), s["c"].data_ptr(), lf.data_ptr(), bits, M, K, N,
+                                 stream.cuda_stream)
+        assert rc == 0, lib.lutgemm_status_string(rc)
+
+    def bwd_gw(s):
+        rc = lib.lutgemm_backward(s["gc"].data_ptr(), s["a"].data_ptr(), s["w"].data_ptr(), None, s["gw"].data_ptr(),
+                                  None, lw.data_ptr(), bits, M, K, N, scratch.data_ptr(), scratch_bytes, stream.cuda_stream)
+        assert rc == 0, lib.lutgemm_status_string(rc)
+
+    def bwd_ga(s):
+        rc = lib.lutgemm_backward(s["gc"].data_ptr(), s["a"].data_ptr(), s["w"].data_ptr(), s["ga"].data_ptr(), None,
+                                  la.data_ptr(), None, bits, M, K, N, None, 0, stream.cuda_stream)
+        assert rc == 0, lib.lutgemm_status_string(rc)
+
+    def step(i, evs=None):
+        s = sets[i % nsets]
+        if evs: evs[0].record()
+        fwd(s)
+        if evs: evs[1].record()
+        bwd_gw(s)
+        if evs: evs[2].record()
+        work = dist.all_reduce(s["gw"], async_op=True) if world > 1 else None  # overlaps the grad_a kernel
+        bwd_ga(s)
+        if work is not None:
+            work.wait()
+        if evs: evs[3].record()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_begin.record()
+    for i in range(args.steps):
+        step(i, evs[i])
+    t_end.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = t_begin.elapsed_time(t_end)
+    if world > 1:
+        t = torch.tensor([total_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    k_ms = np.array([[e[j].elapsed_time(e[j + 1]) for j in range(3)] for e in evs])  # fwd, gw(+allreduce), ga
+    kern_ms = k_ms.mean(axis=0)
+
+    # ---- end-to-end through the reference-facing ops with host buffers --------------------------
+    e2e_steps = max(1, min(args.steps, 5))
+    out_h = {k: torch.empty(sets[0][k].shape, dtype=sets[0][k].dtype).pin_memory() for k in ("c", "ga", "gw")}
+
+    def e2e_step(i):
+        s = sets[i % nsets]
+        a = s["a_h"].to(dev, non_blocking=True)
+        w = s["w_h"].to(dev, non_blocking=True)
+        gc = s["gc_h"].to(dev, non_blocking=True)
+        approx_ops.approx_gemm_forward(a, w, s["c"], lf)
+        approx_ops.approx_gemm_backward(gc, a, w, s["ga"], s["gw"], la, lw)
+        if world > 1:
+            dist.all_reduce(s["gw"])
+        out_h["c"].copy_(s["c"], non_blocking=True)
+        out_h["ga"].copy_(s["ga"], non_blocking=True)
+        out_h["gw"].copy_(s["gw"], non_blocking=True)
+
+    e2e_step(0)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    h2d = M * K + K * N + 4 * M * N
+    d2h = 4 * M * N + 4 * M * K + 4 * K * N
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    macs_step = 3.0 * M * K * N
+    value = world * macs_step * args.steps / (total_ms * 1e-3) / 1e9
+    e2e_value = world * macs_step * e2e_steps / (e2e_ms * 1e-3) / 1e9
+
+    peaks, peaks_kind = measured_peaks()
+    props = torch.cuda.get_device_properties(dev)
+    sms = props.multi_processor_count
+    clk_max = float(peaks.get("sm_max_mhz") or (clocks or {}).get("sm_max_mhz") or 1965.0)
+    clk_seen = (clocks or {}).get("sm_mhz") or clk_max
+    peak_lookups = sms * clk_max * 1e6 * LSU_LOOKUPS_PER_CLK_PER_SM
+    names = ["forward", "grad_w", "grad_a"]
+    dom = int(np.argmax(kern_ms))
+    dom_rate = M * K * N / (kern_ms[dom] * 1e-3)
+    alg_bytes = [M * K + K * N + 4 * M * N, 4 * M * N + M * K + K * N + 4 * K * N, 4 * M * N + M * K + K * N + 4 * M * K]
+    roofline = {
+        "bound": "smem_lsu", "kernel": names[dom], "achieved": dom_rate / 1e9, "peak": peak_lookups / 1e9,
+        "unit": "G lookups/s", "frac": dom_rate / peak_lookups,
+        "peak_def": f"{sms} SMs x {clk_max:.0f} MHz ({peaks_kind} sm_max_mhz) x {LSU_LOOKUPS_PER_CLK_PER_SM} lookups/clk/SM",
+        "frac_at_observed_clock": dom_rate / (sms * clk_seen * 1e6 * LSU_LOOKUPS_PER_CLK_PER_SM),
+        "step_frac": (macs_step * args.steps / (total_ms * 1e-3)) / peak_lookups,
+        "per_kernel_ms": {n: float(t) for n, t in zip(names, kern_ms)},
+        "hbm": {"achieved_gbs": alg_bytes[dom] / (kern_ms[dom] * 1e-3) / 1e9, "peak_gbs": peaks["hbm_gbs"],
+                "frac": alg_bytes[dom] / (kern_ms[dom] * 1e-3) / 1e9 / peaks["hbm_gbs"], "of": peaks_kind},
+        "traffic": None,
+    }
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        lf_n, la_n, lw_n = lf.cpu().numpy(), la.cpu().numpy(), lw.cpu().numpy()
+        rate, cores, rows, secs = cpu_port_rate(bits, K, N, lf_n, la_n, lw_n, w_host.numpy(), target_seconds=12.0, rows_cap=M)
+        cpu = {"value": rate, "unit": "G LUT-MAC/s", "cores": cores, "kind": "port",
+               "sample": f"{rows} of {M} activation rows, full K and N, fwd+bwd, {secs:.1f} s (C/OpenMP port of the "
+                         "reference gather semantics; the reference has no CPU implementation)"}
+
+    line = {
+        "metric": "lut_gemm_fwd_bwd_throughput", "value": value, "unit": "G LUT-MAC/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u16 table -> u32 (fwd) / f32 (bwd) accumulate",
+        "data": "synthetic",
+        "config": {"workload": f"lutgemm fwd+bwd {bits}-bit M=K=N={S} per GPU", "bits": bits, "M_per_gpu": M, "K": K,
+                   "N": N, "parallelism": f"dp{world} (M sharded, NCCL all-reduce of grad_w)" if world > 1 else "single GPU",
+                   "l2": f"{nsets} rotating input/output sets; a step touches {(h2d + d2h) / 2**20:.0f} MiB > L2"},
+        "roofline": roofline, "cpu_baseline": cpu,
+        "e2e": {"value": e2e_value, "unit": "G LUT-MAC/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+        "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--bits", type=int, default=8, choices=[4, 6, 7, 8])
+    ap.add_argument("--size", type=int, default=4096)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

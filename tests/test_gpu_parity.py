@@ -1,0 +1,194 @@
+"""GPU parity tests (run with -m gpu on the B200 box): the CUDA path, called through the C-ABI via the
+`approx_ops` module, against the CPU oracle and the committed golden fixtures.
+
+Forward: bit-exact uint32.  Backward: fp32, tolerance 1e-5 - per element |got - f64| must not exceed
+1e-5 times the sum of the element's absolute terms (the natural scale of an fp32 sum in any order),
+and the max error relative to the largest gradient magnitude must not exceed 1e-5."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle_np as O
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-5
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.fail("gpu-marked test started without a CUDA device")
+    import approx_ops
+    approx_ops.library()  # raises if liblutgemm_b200.so is missing: there is no fallback to test
+    return torch.device("cuda:0")
+
+
+def run_forward(dev, a, w, lut):
+    import approx_ops
+    at, wt = torch.from_numpy(a).to(dev), torch.from_numpy(w).to(dev)
+    c = torch.full((a.shape[0], w.shape[1]), 0xDEADBEEF, dtype=torch.uint32, device=dev)
+    approx_ops.approx_gemm_forward(at, wt, c, torch.from_numpy(lut).to(dev))
+    torch.cuda.synchronize()
+    return c.cpu().numpy()
+
+
+def run_backward(dev, gc, a, w, lut_ga, lut_gw):
+    import approx_ops
+    ga = torch.full(a.shape, float("nan"), dtype=torch.float32, device=dev)
+    gw = torch.full(w.shape, float("nan"), dtype=torch.float32, device=dev)
+    approx_ops.approx_gemm_backward(torch.from_numpy(gc).to(dev), torch.from_numpy(a).to(dev),
+                                    torch.from_numpy(w).to(dev), ga, gw, torch.from_numpy(lut_ga).to(dev),
+                                    torch.from_numpy(lut_gw).to(dev))
+    torch.cuda.synchronize()
+    return ga.cpu().numpy(), gw.cpu().numpy()
+
+
+def check_backward(oracle_c, gc, a, w, lga, lgw, bits, ga, gw):
+    r_ga, r_gw, r_gaa, r_gwa = oracle_c.backward_f64(gc, a, w, lga, lgw, bits)
+    for got, ref, refabs in ((ga, r_ga, r_gaa), (gw, r_gw, r_gwa)):
+        assert np.isfinite(got).all()
+        assert (np.abs(got - ref) <= TOL * refabs + 1e-30).all()
+        assert np.abs(got - ref).max() <= TOL * max(np.abs(ref).max(), 1e-30)
+
+
+def synth_wire(bits, seed=0):
+    return O.to_wire(*O.synthetic_tables(bits, seed=seed), bits)
+
+
+def rand_problem(bits, M, K, N, seed):
+    rng = np.random.default_rng(seed)
+    q = 1 << bits
+    a = rng.integers(0, q, (M, K), dtype=np.uint8) if bits < 8 else rng.integers(0, 256, (M, K)).astype(np.uint8)
+    w = rng.integers(0, q, (K, N), dtype=np.uint8) if bits < 8 else rng.integers(0, 256, (K, N)).astype(np.uint8)
+    gc = rng.standard_normal((M, N)).astype(np.float32)
+    return a, w, gc
+
+
+# ---------------------------------------------------------------------------------------------
+def test_golden_gemm(dev, golden, oracle_c):
+    bits = int(golden["bits"])
+    for i in range(7):
+        a, w, gc = golden[f"gemm{i}_a"], golden[f"gemm{i}_b"], golden[f"gemm{i}_gc"]
+        c = run_forward(dev, a, w, golden["lut_fp"])
+        assert np.array_equal(c.astype(np.float32), golden[f"gemm{i}_c"])
+        assert np.array_equal(c, oracle_c.forward(a, w, golden["lut_fp"], bits))
+        ga, gw = run_backward(dev, gc, a, w, golden["lut_ga"], golden["lut_gb"])
+        check_backward(oracle_c, gc, a, w, golden["lut_ga"], golden["lut_gb"], bits, ga, gw)
+        for got, want in ((ga, golden[f"gemm{i}_ga"]), (gw, golden[f"gemm{i}_gb"])):
+            assert np.abs(got - want).max() <= TOL * max(np.abs(want).max(), 1e-30)
+
+
+RAGGED = [(1, 1, 1), (2, 3, 5), (5, 127, 3), (127, 129, 65), (129, 31, 127), (64, 512, 256), (256, 512, 256),
+          (300, 27, 64), (77, 576, 64), (33, 1152, 128), (50, 200, 300), (513, 16, 10), (16, 2304, 257)]
+
+
+@pytest.mark.parametrize("bits", [4, 6, 7, 8])
+def test_ragged_shapes_all_bit_widths(dev, oracle_c, bits):
+    lf, la, lw = synth_wire(bits, seed=bits)
+    for s, (M, K, N) in enumerate(RAGGED):
+        a, w, gc = rand_problem(bits, M, K, N, seed=100 * bits + s)
+        c = run_forward(dev, a, w, lf)
+        assert np.array_equal(c, oracle_c.forward(a, w, lf, bits)), (bits, M, K, N)
+        ga, gw = run_backward(dev, gc, a, w, la, lw)
+        check_backward(oracle_c, gc, a, w, la, lw, bits, ga, gw)
+
+
+@pytest.mark.parametrize("bits", [7, 8])
+def test_extreme_codes(dev, oracle_c, bits):
+    lf, la, lw = synth_wire(bits, seed=3)
+    q = 1 << bits
+    M, K, N = 96, 160, 272
+    for fill_a, fill_w in ((0, 0), (q - 1, q - 1), (0, q - 1), (q - 1, 0)):
+        a = np.full((M, K), fill_a, np.uint8)
+        w = np.full((K, N), fill_w, np.uint8)
+        gc = np.ones((M, N), np.float32)
+        assert np.array_equal(run_forward(dev, a, w, lf), oracle_c.forward(a, w, lf, bits))
+        ga, gw = run_backward(dev, gc, a, w, la, lw)
+        check_backward(oracle_c, gc, a, w, la, lw, bits, ga, gw)
+
+
+def test_config0_single_layer(dev, oracle_c):
+    """The CPU-runnable benchmark case: M=256, K=512, N=256, 7-bit, seed 0."""
+    bits = 7
+    lf, la, lw = synth_wire(bits, seed=0)
+    a, w, gc = rand_problem(bits, 256, 512, 256, seed=0)
+    assert np.array_equal(run_forward(dev, a, w, lf), oracle_c.forward(a, w, lf, bits))
+    ga, gw = run_backward(dev, gc, a, w, la, lw)
+    check_backward(oracle_c, gc, a, w, la, lw, bits, ga, gw)
+
+
+def test_split_m_weight_gradient_on_a_conv_shape(dev, oracle_c):
+    """A long-M, small-output problem makes the weight-gradient kernel split M into slabs."""
+    bits = 7
+    lf, la, lw = synth_wire(bits, seed=5)
+    a, w, gc = rand_problem(bits, 20000, 72, 64, seed=9)
+    ga, gw = run_backward(dev, gc, a, w, la, lw)
+    check_backward(oracle_c, gc, a, w, la, lw, bits, ga, gw)
+
+
+@pytest.mark.parametrize("bits", [7, 8])
+def test_full_size_properties(dev, oracle_c, bits):
+    """At a benchmark-sized problem the oracle is too slow for every element, so check (1) sampled rows
+    and columns against the oracle, (2) additivity over a split of K (forward is a sum over k),
+    (3) invariance under a joint permutation of k, (4) linearity of the backward in grad_out."""
+    lf, la, lw = synth_wire(bits, seed=1)
+    M = K = N = 2048
+    a, w, gc = rand_problem(bits, M, K, N, seed=77)
+    c = run_forward(dev, a, w, lf)
+    rows = np.array([0, 1, 777, 1024, M - 1])
+    cols = np.array([0, 5, 1000, N - 1])
+    assert np.array_equal(c[rows], oracle_c.forward(a[rows], w, lf, bits))
+    assert np.array_equal(c[:, cols], oracle_c.forward(a, np.ascontiguousarray(w[:, cols]), lf, bits))
+    c1 = run_forward(dev, np.ascontiguousarray(a[:, :1000]), np.ascontiguousarray(w[:1000]), lf)
+    c2 = run_forward(dev, np.ascontiguousarray(a[:, 1000:]), np.ascontiguousarray(w[1000:]), lf)
+    assert np.array_equal(c1 + c2, c)
+    perm = np.random.default_rng(5).permutation(K)
+    assert np.array_equal(run_forward(dev, np.ascontiguousarray(a[:, perm]), np.ascontiguousarray(w[perm]), lf), c)
+
+    ga, gw = run_backward(dev, gc, a, w, la, lw)
+    r_ga, _, r_gaa, _ = oracle_c.backward_f64(gc[rows], a[rows], w, la, lw, bits)
+    assert (np.abs(ga[rows] - r_ga) <= TOL * r_gaa + 1e-30).all()
+    kk = np.array([0, 3, 999, K - 1])
+    _, r_gw, _, r_gwa = oracle_c.backward_f64(gc, np.ascontiguousarray(a[:, kk]), np.ascontiguousarray(w[kk]), la, lw, bits)
+    assert (np.abs(gw[kk] - r_gw) <= TOL * r_gwa + 1e-30).all()
+    ga2, gw2 = run_backward(dev, 2.0 * gc, a, w, la, lw)  # scaling by 2 is exact in fp32
+    assert np.array_equal(ga2, 2.0 * ga) and np.array_equal(gw2, 2.0 * gw)
+
+
+def test_autograd_ops_and_conv_against_golden(dev, golden):
+    """The reference-facing Python ops (self_ops.*) on the GPU against the golden conv fixtures."""
+    import self_ops
+    bits = int(golden["bits"])
+    fp, ga_t, gb_t = (O.unpack_padded(golden[k], bits) for k in ("lut_fp", "lut_ga", "lut_gb"))
+    self_ops.set_lookup_tables(dev, fp, ga_t, gb_t, bits)
+    for i in range(4):
+        B, Cin, H, W, Cout, k, s, p, d = [int(v) for v in golden[f"conv{i}_cfg"]]
+        x = torch.from_numpy(golden[f"conv{i}_x"]).to(dev).float().requires_grad_(True)
+        wt = torch.from_numpy(golden[f"conv{i}_w"]).to(dev).float().requires_grad_(True)
+        y = self_ops.approx_conv2d_op(x, wt, bias=None, stride=(s, s), padding=(p, p), dilation=(d, d), groups=1)
+        assert np.array_equal(y.detach().cpu().numpy(), golden[f"conv{i}_y"])
+        y.backward(torch.from_numpy(golden[f"conv{i}_gy"]).to(dev))
+        for got, want in ((x.grad, golden[f"conv{i}_gx"]), (wt.grad, golden[f"conv{i}_gw"])):
+            got = got.cpu().numpy()
+            assert np.abs(got - want).max() <= TOL * max(np.abs(want).max(), 1e-30)
+    # straight-through variant: same forward, matmul backward
+    a = torch.from_numpy(golden["gemm4_a"]).to(dev).float().requires_grad_(True)
+    b = torch.from_numpy(golden["gemm4_b"]).to(dev).float().requires_grad_(True)
+    c = self_ops.approx_gemm_baseline_op(a, b)
+    assert np.array_equal(c.detach().cpu().numpy(), golden["gemm4_c"])
+    gc = torch.from_numpy(golden["gemm4_gc"]).to(dev)
+    c.backward(gc)
+    assert torch.allclose(a.grad, gc @ b.detach().t(), rtol=1e-4, atol=1e-2)
+
+
+def test_errors_raise_instead_of_printing(dev):
+    import approx_ops
+    a = torch.zeros(4, 4, dtype=torch.uint8, device=dev)
+    c = torch.zeros(4, 4, dtype=torch.uint32, device=dev)
+    with pytest.raises(RuntimeError, match="size should be"):
+        approx_ops.approx_gemm_forward(a, a, c, torch.zeros(1000, dtype=torch.uint16, device=dev))
+    with pytest.raises(RuntimeError, match="shape should be"):
+        approx_ops.approx_gemm_forward(a, a[:3].contiguous(), c, torch.zeros(17408, dtype=torch.uint16, device=dev))
+    with pytest.raises(RuntimeError, match="contiguous"):
+        approx_ops.approx_gemm_forward(a.t(), a, c, torch.zeros(17408, dtype=torch.uint16, device=dev))
