@@ -1,6 +1,7 @@
 // C ABI of liblutgemm_b200.so (declared in include/lutgemm.h): argument validation and dispatch.
 #include <cuda_runtime.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "lutgemm.h"
@@ -65,6 +66,16 @@ int lutgemm_forward(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint1
     if ((reinterpret_cast<uintptr_t>(c) & 3) || (reinterpret_cast<uintptr_t>(lut) & 1)) return LUTGEMM_E_BADARG;
     const int sms = current_num_sms();
     if (sms <= 0) return LUTGEMM_E_CUDA;
+    // Large-M problems with reasonably filled 512x64 tiles go to the slab kernel; small or skinny ones
+    // to the row-broadcast kernel.  LUTGEMM_FORWARD_KERNEL=rowbcast|slab overrides (for A/B timing).
+    const long tm = (M + 511) / 512, tn = (N + 63) / 64;
+    const double fill = (double)M * N / ((double)tm * 512 * tn * 64);
+    bool slab = M >= 512 && N >= 32 && fill >= 0.6;
+    if (const char *force = getenv("LUTGEMM_FORWARD_KERNEL")) {
+        if (!strcmp(force, "rowbcast")) slab = false;
+        if (!strcmp(force, "slab")) slab = true;
+    }
+    if (slab) return lutgemm::forward_slab(a, w, c, lut, bits, M, K, N, sms, static_cast<cudaStream_t>(stream));
     return lutgemm::forward_rowbcast(a, w, c, lut, bits, M, K, N, sms, static_cast<cudaStream_t>(stream));
 }
 

@@ -10,6 +10,9 @@ namespace lutgemm {
 int forward_rowbcast(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K,
                      int N, int num_sms, cudaStream_t stream);
 
+int forward_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K, int N,
+                 int num_sms, cudaStream_t stream);
+
 // number of slabs the weight-gradient kernel splits M into (1 = no scratch needed)
 int gw_num_splits(int bits, int M, int K, int N, int num_sms);
 

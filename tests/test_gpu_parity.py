@@ -80,7 +80,8 @@ def test_golden_gemm(dev, golden, oracle_c):
 
 
 RAGGED = [(1, 1, 1), (2, 3, 5), (5, 127, 3), (127, 129, 65), (129, 31, 127), (64, 512, 256), (256, 512, 256),
-          (300, 27, 64), (77, 576, 64), (33, 1152, 128), (50, 200, 300), (513, 16, 10), (16, 2304, 257)]
+          (300, 27, 64), (77, 576, 64), (33, 1152, 128), (50, 200, 300), (513, 16, 10), (16, 2304, 257),
+          (700, 45, 70), (1025, 130, 33), (512, 16, 64), (2100, 300, 200), (1536, 17, 96)]
 
 
 @pytest.mark.parametrize("bits", [4, 6, 7, 8])
@@ -92,6 +93,18 @@ def test_ragged_shapes_all_bit_widths(dev, oracle_c, bits):
         assert np.array_equal(c, oracle_c.forward(a, w, lf, bits)), (bits, M, K, N)
         ga, gw = run_backward(dev, gc, a, w, la, lw)
         check_backward(oracle_c, gc, a, w, la, lw, bits, ga, gw)
+
+
+@pytest.mark.parametrize("kernel", ["rowbcast", "slab"])
+@pytest.mark.parametrize("bits", [4, 6, 7, 8])
+def test_each_forward_kernel_on_every_shape_class(dev, oracle_c, bits, kernel, monkeypatch):
+    """Both forward kernels (selected through LUTGEMM_FORWARD_KERNEL) must be bit-exact on shapes the
+    dispatcher would normally send to the other one, including tiles that are almost empty."""
+    monkeypatch.setenv("LUTGEMM_FORWARD_KERNEL", kernel)
+    lf, _, _ = synth_wire(bits, seed=10 + bits)
+    for s, (M, K, N) in enumerate([(1, 1, 1), (5, 33, 3), (130, 16, 64), (515, 31, 67), (1024, 48, 128), (600, 257, 65)]):
+        a, w, _ = rand_problem(bits, M, K, N, seed=7 * bits + s)
+        assert np.array_equal(run_forward(dev, a, w, lf), oracle_c.forward(a, w, lf, bits)), (kernel, bits, M, K, N)
 
 
 @pytest.mark.parametrize("bits", [7, 8])
