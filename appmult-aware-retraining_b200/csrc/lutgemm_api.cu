@@ -25,6 +25,49 @@ int current_num_sms() {
 
 thread_local char g_msg[256];
 
+// tile fill of a [rows x cols] problem cut into 512 x 64 slab tiles
+double slab_fill(long rows, long cols) {
+    const long tr = (rows + 511) / 512, tc = (cols + 63) / 64;
+    return (double)rows * (double)cols / ((double)tr * 512.0 * (double)tc * 64.0);
+}
+
+bool env_is(const char *name, const char *value) {
+    const char *e = getenv(name);
+    return e && !strcmp(e, value);
+}
+
+struct BackwardPlan {
+    bool gw_slab, ga_slab;
+    int gw_splits;        // row-broadcast grad_w kernel: slabs of M
+    size_t gw_scratch, ga_scratch;
+};
+
+// Kernel choice for the two gradients.  Slab kernels amortise one slab build over 512 rows of the
+// reduction dimension (M for grad_w, N for grad_a), so they need that dimension long and the tiles
+// reasonably full; everything else goes to the row/column-broadcast kernels.
+// LUTGEMM_BACKWARD_KERNEL=bcast|slab overrides (for A/B timing).
+BackwardPlan plan_backward(int bits, int M, int K, int N, int sms) {
+    BackwardPlan pl{};
+    // measured on B200 at 4096^3: the gradient slab kernels beat the broadcast kernels only where the
+    // latter suffer bank conflicts (7 and 8 bits); at 4 and 6 bits a table row is conflict-free already
+    pl.gw_slab = bits >= 7 && M >= 512 && N >= 32 && slab_fill(M, N) >= 0.6;
+    pl.ga_slab = bits >= 7 && N >= 384 && M >= 32 && slab_fill(N, M) >= 0.6;
+    if (env_is("LUTGEMM_BACKWARD_KERNEL", "bcast")) pl.gw_slab = pl.ga_slab = false;
+    if (env_is("LUTGEMM_BACKWARD_KERNEL", "slab")) pl.gw_slab = pl.ga_slab = true;
+    pl.gw_splits = pl.gw_slab ? 1 : lutgemm::gw_num_splits(bits, M, K, N, sms);
+    if (pl.gw_slab) {
+        const int rb = lutgemm::slab_grad_row_blocks(M);
+        pl.gw_scratch = rb > 1 ? (size_t)rb * K * N * sizeof(float) : 0;
+    } else {
+        pl.gw_scratch = pl.gw_splits > 1 ? (size_t)pl.gw_splits * K * N * sizeof(float) : 0;
+    }
+    if (pl.ga_slab) {
+        const int rb = lutgemm::slab_grad_row_blocks(N);
+        pl.ga_scratch = rb > 1 ? (size_t)rb * K * M * sizeof(float) : 0;
+    }
+    return pl;
+}
+
 }  // namespace
 
 extern "C" {
@@ -83,8 +126,8 @@ size_t lutgemm_backward_scratch_bytes(int bits, int M, int K, int N) {
     if (!lutgemm::bits_supported(bits) || M <= 0 || K <= 0 || N <= 0) return 0;
     const int sms = current_num_sms();
     if (sms <= 0) return 0;
-    const int splits = lutgemm::gw_num_splits(bits, M, K, N, sms);
-    return splits > 1 ? (size_t)splits * K * N * sizeof(float) : 0;
+    const BackwardPlan pl = plan_backward(bits, M, K, N, sms);
+    return pl.gw_scratch > pl.ga_scratch ? pl.gw_scratch : pl.ga_scratch;
 }
 
 int lutgemm_backward(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, float *gw,
@@ -100,16 +143,19 @@ int lutgemm_backward(const float *gc, const uint8_t *a, const uint8_t *w, float 
     const int sms = current_num_sms();
     if (sms <= 0) return LUTGEMM_E_CUDA;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const BackwardPlan pl = plan_backward(bits, M, K, N, sms);
+    float *sc = static_cast<float *>(scratch);
     if (gw) {
         // the weight gradient goes first: under data parallelism its all-reduce can then overlap gA
-        const int splits = lutgemm::gw_num_splits(bits, M, K, N, sms);
-        if (splits > 1 && (!scratch || scratch_bytes < (size_t)splits * K * N * sizeof(float)))
-            return LUTGEMM_E_SCRATCH;
-        int rc = lutgemm::backward_gw(gc, a, w, gw, lut_gw, bits, M, K, N, static_cast<float *>(scratch), splits, sms, s);
+        if (pl.gw_scratch && (!scratch || scratch_bytes < pl.gw_scratch)) return LUTGEMM_E_SCRATCH;
+        int rc = pl.gw_slab ? lutgemm::backward_gw_slab(gc, a, w, gw, lut_gw, bits, M, K, N, sc, sms, s)
+                            : lutgemm::backward_gw(gc, a, w, gw, lut_gw, bits, M, K, N, sc, pl.gw_splits, sms, s);
         if (rc != LUTGEMM_OK) return rc;
     }
     if (ga) {
-        int rc = lutgemm::backward_ga(gc, a, w, ga, lut_ga, bits, M, K, N, sms, s);
+        if (pl.ga_scratch && (!scratch || scratch_bytes < pl.ga_scratch)) return LUTGEMM_E_SCRATCH;
+        int rc = pl.ga_slab ? lutgemm::backward_ga_slab(gc, a, w, ga, lut_ga, bits, M, K, N, sc, sms, s)
+                            : lutgemm::backward_ga(gc, a, w, ga, lut_ga, bits, M, K, N, sms, s);
         if (rc != LUTGEMM_OK) return rc;
     }
     return LUTGEMM_OK;

@@ -218,7 +218,7 @@ def run_ours(args, rank, world, local_rank):
         })
     scratch_bytes = lib.lutgemm_backward_scratch_bytes(bits, M, K, N)
     scratch = torch.empty(max(1, scratch_bytes), dtype=torch.uint8, device=dev)
-    launches_per_step = 3 + (1 if scratch_bytes else 0)
+    launches_per_step = 3 + (2 if scratch_bytes else 0)  # + the two block-reduce kernels
     stream = torch.cuda.current_stream(dev)
 
     def fwd(s):
@@ -233,7 +233,7 @@ def run_ours(args, rank, world, local_rank):
 
     def bwd_ga(s):
         rc = lib.lutgemm_backward(s["gc"].data_ptr(), s["a"].data_ptr(), s["w"].data_ptr(), s["ga"].data_ptr(), None,
-                                  la.data_ptr(), None, bits, M, K, N, None, 0, stream.cuda_stream)
+                                  la.data_ptr(), None, bits, M, K, N, scratch.data_ptr(), scratch_bytes, stream.cuda_stream)
         assert rc == 0, lib.lutgemm_status_string(rc)
 
     def step(i, evs=None):

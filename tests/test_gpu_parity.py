@@ -81,7 +81,8 @@ def test_golden_gemm(dev, golden, oracle_c):
 
 RAGGED = [(1, 1, 1), (2, 3, 5), (5, 127, 3), (127, 129, 65), (129, 31, 127), (64, 512, 256), (256, 512, 256),
           (300, 27, 64), (77, 576, 64), (33, 1152, 128), (50, 200, 300), (513, 16, 10), (16, 2304, 257),
-          (700, 45, 70), (1025, 130, 33), (512, 16, 64), (2100, 300, 200), (1536, 17, 96)]
+          (700, 45, 70), (1025, 130, 33), (512, 16, 64), (2100, 300, 200), (1536, 17, 96),
+          (100, 50, 600), (70, 33, 1030), (513, 20, 512), (1100, 40, 1100)]
 
 
 @pytest.mark.parametrize("bits", [4, 6, 7, 8])
@@ -105,6 +106,18 @@ def test_each_forward_kernel_on_every_shape_class(dev, oracle_c, bits, kernel, m
     for s, (M, K, N) in enumerate([(1, 1, 1), (5, 33, 3), (130, 16, 64), (515, 31, 67), (1024, 48, 128), (600, 257, 65)]):
         a, w, _ = rand_problem(bits, M, K, N, seed=7 * bits + s)
         assert np.array_equal(run_forward(dev, a, w, lf), oracle_c.forward(a, w, lf, bits)), (kernel, bits, M, K, N)
+
+
+@pytest.mark.parametrize("kernel", ["bcast", "slab"])
+@pytest.mark.parametrize("bits", [4, 6, 7, 8])
+def test_each_backward_kernel_on_every_shape_class(dev, oracle_c, bits, kernel, monkeypatch):
+    """Both families of gradient kernels (LUTGEMM_BACKWARD_KERNEL) on shapes of either class."""
+    monkeypatch.setenv("LUTGEMM_BACKWARD_KERNEL", kernel)
+    _, la, lw = synth_wire(bits, seed=20 + bits)
+    for s, (M, K, N) in enumerate([(1, 1, 1), (5, 33, 3), (130, 16, 64), (515, 31, 67), (1024, 48, 128), (66, 35, 520)]):
+        a, w, gc = rand_problem(bits, M, K, N, seed=11 * bits + s)
+        ga, gw = run_backward(dev, gc, a, w, la, lw)
+        check_backward(oracle_c, gc, a, w, la, lw, bits, ga, gw)
 
 
 @pytest.mark.parametrize("bits", [7, 8])
