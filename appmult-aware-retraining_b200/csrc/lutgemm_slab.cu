@@ -66,9 +66,14 @@ struct SlabArgs {
     int ksplits, k_per_split;  // forward only
     int direct;                // gradients: 1 = single row block, write the scaled result in place
     int vec_a, vec_w, vec_o, vec_g;
+    // constants handed over as run-time values so that the compiler keeps the multiply-add forms that run
+    // on the FMA pipe (the integer ALU pipe is the scarcer one in the use phase)
+    uint32_t c_row_bytes;  // U_STRIDE * 4
+    uint32_t c_64k;        // 65536
 };
 
-// ACC (forward): 0 = two dp2a per word; 1 = full-word add plus shifted add, fixed up at the end.
+// ACC (forward): 0 = two dp2a per word; 1 = full-word add plus shifted add, fixed up at the end;
+// 2 = as 1 but the slab-row address and the high-half add are integer multiply-adds (FMA pipe).
 template <int BITS, int MODE, int ACC>
 __global__ void __launch_bounds__(512, 1) slab_kernel(const SlabArgs p) {
     using Cfg = SlabCfg<BITS>;
@@ -314,16 +319,25 @@ __global__ void __launch_bounds__(512, 1) slab_kernel(const SlabArgs p) {
             float s0a = 0.f, s0b = 0.f, s1a = 0.f, s1b = 0.f;
 #pragma unroll
             for (int r = 0; r < 32; ++r) {
-                const uint32_t x = byte_of(rv[r >> 2], r & 3);
-                uint32_t word;
-                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(word) : "r"(ub + x * (US * 4)));
+                uint32_t x, addr, word;
+                if constexpr (ACC == 2) {
+                    x = __byte_perm(rv[r >> 2], 0u, 0x4440u + (r & 3));
+                    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(addr) : "r"(x), "r"(p.c_row_bytes), "r"(ub));
+                } else {
+                    x = byte_of(rv[r >> 2], r & 3);
+                    addr = ub + x * (US * 4);
+                }
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(word) : "r"(addr));
                 if (MODE == kFwd) {
                     if constexpr (ACC == 0) {
                         acc[r][0] = __dp2a_lo(word, 0x00000001u, acc[r][0]);
                         acc[r][1] = __dp2a_lo(word, 0x00000100u, acc[r][1]);
-                    } else {
+                    } else if constexpr (ACC == 1) {
                         acc[r][0] += word;
                         acc[r][1] += word >> 16;
+                    } else {
+                        acc[r][0] += word;
+                        asm("mad.hi.u32 %0, %1, %2, %0;" : "+r"(acc[r][1]) : "r"(word), "r"(p.c_64k));
                     }
                 } else {
                     const float f0 = (float)(int16_t)(word & 0xffffu);
@@ -447,16 +461,19 @@ static int launch_fwd_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, cons
     p.vec_a = (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(a) & 15) == 0);
     p.vec_w = (N % 16 == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
     p.vec_o = (N % 2 == 0) && ((reinterpret_cast<uintptr_t>(c) & 7) == 0);
+    p.c_row_bytes = Cfg::U_STRIDE * 4;
+    p.c_64k = 65536u;
     kern<<<grid, Cfg::THREADS, Cfg::SMEM_FWD, stream>>>(p);
     return cudaGetLastError() == cudaSuccess ? LUTGEMM_OK : LUTGEMM_E_CUDA;
 }
 
 int forward_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K, int N,
                  int num_sms, cudaStream_t stream) {
-    const int acc = env_int("LUTGEMM_SLAB_ACC", 1);
+    const int acc = env_int("LUTGEMM_SLAB_ACC", 1);  // 1 measured fastest on B200 (0: +6 %, 2: +45 % time)
 #define LUTGEMM_CASE(B)                                                                         \
     case B:                                                                                     \
         if (acc == 0) return launch_fwd_slab<B, 0>(a, w, c, lut, M, K, N, num_sms, stream);     \
+        if (acc == 2) return launch_fwd_slab<B, 2>(a, w, c, lut, M, K, N, num_sms, stream);     \
         return launch_fwd_slab<B, 1>(a, w, c, lut, M, K, N, num_sms, stream);
     switch (bits) {
         LUTGEMM_CASE(4)
@@ -489,6 +506,8 @@ static int launch_grad_slab(const float *gc, const uint8_t *a, const uint8_t *w,
     p.vec_a = (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(a) & 15) == 0);
     p.vec_w = (N % 16 == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
     p.vec_g = (N % 4 == 0) && ((reinterpret_cast<uintptr_t>(gc) & 15) == 0);
+    p.c_row_bytes = Cfg::U_STRIDE * 4;
+    p.c_64k = 65536u;
     const long items = (long)p.tiles_r * p.tiles_c;
     const int grid = (int)(items < num_sms ? items : num_sms);
     kern<<<grid, Cfg::THREADS, Cfg::SMEM_BWD, stream>>>(p);
