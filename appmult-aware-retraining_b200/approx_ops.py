@@ -50,6 +50,10 @@ def _load():
     lib.lutgemm_backward_scratch_bytes.argtypes = [ci, ci, ci, ci]
     lib.lutgemm_backward.restype = ci
     lib.lutgemm_backward.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp, sz, vp]
+    lib.lutgemm_device_error.restype = ci
+    lib.lutgemm_device_error.argtypes = [ctypes.POINTER(ci)]
+    lib.lutgemm_selftest_bounded_wait.restype = ci
+    lib.lutgemm_selftest_bounded_wait.argtypes = [vp]
     _lib = lib
     return lib
 
@@ -57,6 +61,14 @@ def _load():
 def library():
     """The loaded ctypes handle of liblutgemm_b200.so (raises if it has not been built)."""
     return _load()
+
+
+def device_error() -> int:
+    """Reads and clears the device-side error word of the pipelined kernels (0 = no error).  A non-zero
+    value names the bounded barrier wait that ran out; results since the last call are then invalid."""
+    v = ctypes.c_int(0)
+    _check(_load().lutgemm_device_error(ctypes.byref(v)), "lutgemm_device_error")
+    return v.value
 
 
 def _check(status: int, what: str) -> None:

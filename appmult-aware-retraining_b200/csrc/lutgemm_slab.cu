@@ -102,7 +102,8 @@ __global__ void __launch_bounds__(512, 1) slab_kernel(const SlabArgs p) {
         uint16_t *tt16 = reinterpret_cast<uint16_t *>(tt_s);
         for (int idx = tid; idx < Q * Q; idx += THREADS) {
             const int hi_idx = idx >> BITS, lo_idx = idx & (Q - 1);  // global read is contiguous in lo_idx
-            const uint16_t v = lut[hi_idx * COL + lo_idx];
+            uint16_t v = lut[hi_idx * COL + lo_idx];
+            if (MODE != kFwd && ACC == 1) v ^= 0x8000u;  // offset-binary: u = v + 32768 for the magic-number conversion
             const int x = MODE == kGa ? lo_idx : hi_idx, y = MODE == kGa ? hi_idx : lo_idx;
             tt16[(y * TTS + (x & (HALF - 1))) * 2 + (x >> (BITS - 1))] = v;
         }
@@ -335,13 +336,25 @@ __global__ void __launch_bounds__(512, 1) slab_kernel(const SlabArgs p) {
                     } else if constexpr (ACC == 1) {
                         acc[r][0] += word;
                         acc[r][1] += word >> 16;
+                    } else if constexpr (ACC == 3) {
+                        acc[r][0] += word;
+                        acc[r][1] = __dp2a_lo(word, 0x00000100u, acc[r][1]);
                     } else {
                         acc[r][0] += word;
                         asm("mad.hi.u32 %0, %1, %2, %0;" : "+r"(acc[r][1]) : "r"(word), "r"(p.c_64k));
                     }
                 } else {
-                    const float f0 = (float)(int16_t)(word & 0xffffu);
-                    const float f1 = (float)((int32_t)word >> 16);
+                    float f0, f1;
+                    if constexpr (ACC == 1) {
+                        // 0x4B000000 | u is the float 2^23 + u; subtracting 2^23 + 32768 leaves the signed
+                        // entry exactly.  One logic op + one FADD per value instead of a conversion on
+                        // the (16 lanes/clk) XU pipe.
+                        f0 = __uint_as_float((word & 0xffffu) | 0x4B000000u) - 8421376.0f;
+                        f1 = __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7632)) - 8421376.0f;
+                    } else {
+                        f0 = (float)(int16_t)(word & 0xffffu);
+                        f1 = (float)((int32_t)word >> 16);
+                    }
                     if (r & 1) { s0b = fmaf(f0, g[r][0], s0b); s1b = fmaf(f1, g[r][1], s1b); }
                     else       { s0a = fmaf(f0, g[r][0], s0a); s1a = fmaf(f1, g[r][1], s1a); }
                 }
@@ -357,7 +370,7 @@ __global__ void __launch_bounds__(512, 1) slab_kernel(const SlabArgs p) {
             const int n = c0 + 2 * lane;
 #pragma unroll
             for (int r = 0; r < 32; ++r) {
-                if constexpr (ACC != 0) acc[r][0] -= acc[r][1] << 16;
+                if constexpr (ACC != 0) acc[r][0] -= acc[r][1] << 16;  // low sum = full-word sum - 65536 * high sum
                 const int m = r0 + wp * 32 + r;
                 if (m < M) {
                     uint32_t *crow = reinterpret_cast<uint32_t *>(p.out) + (size_t)m * N;
@@ -474,6 +487,7 @@ int forward_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t
     case B:                                                                                     \
         if (acc == 0) return launch_fwd_slab<B, 0>(a, w, c, lut, M, K, N, num_sms, stream);     \
         if (acc == 2) return launch_fwd_slab<B, 2>(a, w, c, lut, M, K, N, num_sms, stream);     \
+        if (acc == 3) return launch_fwd_slab<B, 3>(a, w, c, lut, M, K, N, num_sms, stream);     \
         return launch_fwd_slab<B, 1>(a, w, c, lut, M, K, N, num_sms, stream);
     switch (bits) {
         LUTGEMM_CASE(4)
@@ -485,6 +499,15 @@ int forward_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t
     return LUTGEMM_E_BITS;
 }
 
+int slab_reduce_blocks(const float *part, float *out, int K, int C, int nblocks, bool transpose, int num_sms,
+                       cudaStream_t stream) {
+    const long tiles = (long)((K + 31) / 32) * ((C + 31) / 32);
+    const int rgrid = (int)(tiles < 8L * num_sms ? tiles : 8L * num_sms);
+    if (transpose) slab_reduce_blocks_kernel<true><<<rgrid, 256, 0, stream>>>(part, out, K, C, nblocks, kGradFactor);
+    else slab_reduce_blocks_kernel<false><<<rgrid, 256, 0, stream>>>(part, out, K, C, nblocks, kGradFactor);
+    return cudaGetLastError() == cudaSuccess ? LUTGEMM_OK : LUTGEMM_E_CUDA;
+}
+
 // number of 512-row blocks of the reduction dimension (M for grad_w, N for grad_a)
 int slab_grad_row_blocks(int rdim) { return (rdim + 511) / 512; }
 
@@ -492,7 +515,7 @@ template <int BITS, int MODE>
 static int launch_grad_slab(const float *gc, const uint8_t *a, const uint8_t *w, float *out, const int16_t *lut,
                             int M, int K, int N, float *scratch, int num_sms, cudaStream_t stream) {
     using Cfg = SlabCfg<BITS>;
-    auto kern = slab_kernel<BITS, MODE, 0>;
+    auto kern = env_int("LUTGEMM_SLAB_CVT", 1) == 0 ? slab_kernel<BITS, MODE, 0> : slab_kernel<BITS, MODE, 1>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BWD) != cudaSuccess)
         return LUTGEMM_E_CUDA;
     const int RDIM = MODE == kGa ? N : M, CDIM = MODE == kGa ? M : N;
@@ -512,15 +535,7 @@ static int launch_grad_slab(const float *gc, const uint8_t *a, const uint8_t *w,
     const int grid = (int)(items < num_sms ? items : num_sms);
     kern<<<grid, Cfg::THREADS, Cfg::SMEM_BWD, stream>>>(p);
     if (cudaGetLastError() != cudaSuccess) return LUTGEMM_E_CUDA;
-    if (!p.direct) {
-        const long tiles = (long)((K + 31) / 32) * ((CDIM + 31) / 32);
-        const int rgrid = (int)(tiles < 8L * num_sms ? tiles : 8L * num_sms);
-        if (MODE == kGa)
-            slab_reduce_blocks_kernel<true><<<rgrid, 256, 0, stream>>>(scratch, out, K, CDIM, p.tiles_r, kGradFactor);
-        else
-            slab_reduce_blocks_kernel<false><<<rgrid, 256, 0, stream>>>(scratch, out, K, CDIM, p.tiles_r, kGradFactor);
-        if (cudaGetLastError() != cudaSuccess) return LUTGEMM_E_CUDA;
-    }
+    if (!p.direct) return slab_reduce_blocks(scratch, out, K, CDIM, p.tiles_r, MODE == kGa, num_sms, stream);
     return LUTGEMM_OK;
 }
 

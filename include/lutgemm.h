@@ -79,6 +79,24 @@ int lutgemm_backward(const float *gc, const uint8_t *a, const uint8_t *w, float 
                      const int16_t *lut_ga, const int16_t *lut_gw, int bits, int M, int K, int N,
                      void *scratch, size_t scratch_bytes, void *stream);
 
+/*
+ * Reads and clears the device-side error word of the pipelined kernels into *value (0 = no error).
+ * Their warps hand slabs to each other through shared-memory barriers; every wait on such a barrier is
+ * bounded, and a wait that runs out records which one it was instead of hanging the GPU.  A non-zero
+ * value means the results of launches since the last call are invalid.  Synchronises the device.
+ * No counterpart in the reference (its kernels have no inter-warp waits).
+ */
+int lutgemm_device_error(int *value);
+
+/*
+ * Launches a one-warp kernel that waits on a shared-memory barrier nothing ever arrives on.  The wait
+ * is bounded like every wait in the library: it gives up after a fraction of a second, records error
+ * id 99 (readable through lutgemm_device_error) and the kernel returns; the context stays usable.
+ * Exists so that the time-out path can be exercised without hanging a GPU.  No counterpart in the
+ * reference.
+ */
+int lutgemm_selftest_bounded_wait(void *stream);
+
 #ifdef __cplusplus
 }
 #endif

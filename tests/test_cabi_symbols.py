@@ -32,7 +32,8 @@ def lib():
 def test_header_declares_the_expected_entry_points():
     syms = declared_symbols()
     for s in ("lutgemm_forward", "lutgemm_backward", "lutgemm_backward_scratch_bytes", "lutgemm_lut_elem_num",
-              "lutgemm_bits_from_elem_num", "lutgemm_status_string", "lutgemm_version"):
+              "lutgemm_bits_from_elem_num", "lutgemm_status_string", "lutgemm_version", "lutgemm_device_error",
+              "lutgemm_selftest_bounded_wait"):
         assert s in syms
 
 

@@ -96,23 +96,25 @@ def test_ragged_shapes_all_bit_widths(dev, oracle_c, bits):
         check_backward(oracle_c, gc, a, w, la, lw, bits, ga, gw)
 
 
-@pytest.mark.parametrize("kernel", ["rowbcast", "slab"])
+@pytest.mark.parametrize("kernel", ["rowbcast", "slab", "slab-ws"])
 @pytest.mark.parametrize("bits", [4, 6, 7, 8])
 def test_each_forward_kernel_on_every_shape_class(dev, oracle_c, bits, kernel, monkeypatch):
-    """Both forward kernels (selected through LUTGEMM_FORWARD_KERNEL) must be bit-exact on shapes the
-    dispatcher would normally send to the other one, including tiles that are almost empty."""
-    monkeypatch.setenv("LUTGEMM_FORWARD_KERNEL", kernel)
+    """Every forward kernel (selected through LUTGEMM_FORWARD_KERNEL / LUTGEMM_SLAB_IMPL) must be bit-exact
+    on shapes the dispatcher would normally send to another one, including tiles that are almost empty."""
+    monkeypatch.setenv("LUTGEMM_FORWARD_KERNEL", kernel.split("-")[0])
+    monkeypatch.setenv("LUTGEMM_SLAB_IMPL", "ws" if kernel.endswith("-ws") else "sync")
     lf, _, _ = synth_wire(bits, seed=10 + bits)
     for s, (M, K, N) in enumerate([(1, 1, 1), (5, 33, 3), (130, 16, 64), (515, 31, 67), (1024, 48, 128), (600, 257, 65)]):
         a, w, _ = rand_problem(bits, M, K, N, seed=7 * bits + s)
         assert np.array_equal(run_forward(dev, a, w, lf), oracle_c.forward(a, w, lf, bits)), (kernel, bits, M, K, N)
 
 
-@pytest.mark.parametrize("kernel", ["bcast", "slab"])
+@pytest.mark.parametrize("kernel", ["bcast", "slab", "slab-ws"])
 @pytest.mark.parametrize("bits", [4, 6, 7, 8])
 def test_each_backward_kernel_on_every_shape_class(dev, oracle_c, bits, kernel, monkeypatch):
-    """Both families of gradient kernels (LUTGEMM_BACKWARD_KERNEL) on shapes of either class."""
-    monkeypatch.setenv("LUTGEMM_BACKWARD_KERNEL", kernel)
+    """Every family of gradient kernels (LUTGEMM_BACKWARD_KERNEL / LUTGEMM_SLAB_IMPL) on shapes of either class."""
+    monkeypatch.setenv("LUTGEMM_BACKWARD_KERNEL", kernel.split("-")[0])
+    monkeypatch.setenv("LUTGEMM_SLAB_IMPL", "ws" if kernel.endswith("-ws") else "sync")
     _, la, lw = synth_wire(bits, seed=20 + bits)
     for s, (M, K, N) in enumerate([(1, 1, 1), (5, 33, 3), (130, 16, 64), (515, 31, 67), (1024, 48, 128), (66, 35, 520)]):
         a, w, gc = rand_problem(bits, M, K, N, seed=11 * bits + s)
@@ -218,3 +220,16 @@ def test_errors_raise_instead_of_printing(dev):
         approx_ops.approx_gemm_forward(a, a[:3].contiguous(), c, torch.zeros(17408, dtype=torch.uint16, device=dev))
     with pytest.raises(RuntimeError, match="contiguous"):
         approx_ops.approx_gemm_forward(a.t(), a, c, torch.zeros(17408, dtype=torch.uint16, device=dev))
+
+
+def test_bounded_wait_times_out_and_reports(dev):
+    """A barrier wait that can never be satisfied must give up, report its id through the error word and
+    leave the context usable (no hang, no fault)."""
+    import approx_ops
+    assert approx_ops.device_error() == 0  # nothing above ran into a time-out
+    assert approx_ops.library().lutgemm_selftest_bounded_wait(None) == 0
+    torch.cuda.synchronize()
+    assert approx_ops.device_error() == 99
+    assert approx_ops.device_error() == 0  # reading clears it
+    x = torch.ones(8, device=dev)
+    assert float(x.sum()) == 8.0
