@@ -80,6 +80,29 @@ int lutgemm_backward(const float *gc, const uint8_t *a, const uint8_t *w, float 
                      void *scratch, size_t scratch_bytes, void *stream);
 
 /*
+ * Weight gradient only, with no device memory taken from anyone: same result as lutgemm_backward with
+ * ga == NULL, but the kernels' partial sums go to a fixed array inside the library image instead of a
+ * caller-supplied scratch buffer.  Meant for callers that may not allocate when the gradient is due -
+ * a runtime with a memory budget fixed at start-up, a binding that cannot reach the framework's
+ * allocator, code on a path where cudaMalloc's implicit synchronisation is not acceptable.
+ *   - The array is LUTGEMM_NOALLOC_SCRATCH_BYTES (32 MiB) per GPU that loads the library, held until
+ *     the process exits; lutgemm_noalloc_scratch_capacity() returns the figure.  A problem whose partial
+ *     sums need more is refused with LUTGEMM_E_TOOLARGE (they need ceil(M/512)*K*N*4 bytes on the slab
+ *     path, splits*K*N*4 on the split-M path, nothing for small M).
+ *   - The first call made with a given device current looks up the array's address on that device
+ *     (cudaGetSymbolAddress); make that first call before any stream capture begins.
+ *   - All calls share the one array per device and it keeps whatever the last call left there.  Nothing
+ *     in it has to be zero on entry (every partial sum is written before it is read).  Two calls that
+ *     overlap on the same GPU - different streams, or different host threads - race on it: serialise them.
+ *   - The call itself performs no cudaMalloc / cudaFree and uses no allocating library routine.
+ * No counterpart in the reference.
+ */
+#define LUTGEMM_NOALLOC_SCRATCH_BYTES (32u << 20)
+size_t lutgemm_noalloc_scratch_capacity(void);
+int lutgemm_backward_gw_noalloc(const float *gc, const uint8_t *a, const uint8_t *w, float *gw,
+                                const int16_t *lut_gw, int bits, int M, int K, int N, void *stream);
+
+/*
  * Reads and clears the device-side error word of the pipelined kernels into *value (0 = no error).
  * Their warps hand slabs to each other through shared-memory barriers; every wait on such a barrier is
  * bounded, and a wait that runs out records which one it was instead of hanging the GPU.  A non-zero
