@@ -50,6 +50,12 @@ def _load():
     lib.lutgemm_backward_scratch_bytes.argtypes = [ci, ci, ci, ci]
     lib.lutgemm_backward.restype = ci
     lib.lutgemm_backward.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp, sz, vp]
+    lib.lutgemm_conv2d_forward.restype = ci
+    lib.lutgemm_conv2d_forward.argtypes = [vp, vp, vp, vp] + [ci] * 11 + [vp]
+    lib.lutgemm_conv2d_backward_scratch_bytes.restype = sz
+    lib.lutgemm_conv2d_backward_scratch_bytes.argtypes = [ci] * 11
+    lib.lutgemm_conv2d_backward.restype = ci
+    lib.lutgemm_conv2d_backward.argtypes = [vp] * 7 + [ci] * 11 + [vp, sz, vp]
     lib.lutgemm_device_error.restype = ci
     lib.lutgemm_device_error.argtypes = [ctypes.POINTER(ci)]
     lib.lutgemm_selftest_bounded_wait.restype = ci
@@ -184,3 +190,69 @@ def acc_gemm_forward_fp32(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor) -> 
     if tuple(c.shape) != (a.shape[0], b.shape[1]):
         raise RuntimeError(f"c_tensor's shape should be {a.shape[0]} x {b.shape[1]}")
     torch.mm(a, b, out=c)
+
+
+def _conv_out(H, W, kh, kw, stride, pad, dil):
+    return (H + 2 * pad - dil * (kh - 1) - 1) // stride + 1, (W + 2 * pad - dil * (kw - 1) - 1) // stride + 1
+
+
+def approx_conv2d_forward(x: torch.Tensor, wmat: torch.Tensor, y: torch.Tensor, lut: torch.Tensor, kh: int, kw: int,
+                          stride: int, pad: int, dil: int) -> None:
+    """Fused-im2col convolution forward.  x: u8 codes [B,C,H,W]; wmat: u8 [C*kh*kw, Cout]; y: u32
+    [B*Ho*Wo, Cout] (NHWC), written in place.  The reference declares such an op
+    (`approx_conv2d_forward`, self_ops/src/op_register.cpp:11,22) but ships no source for it."""
+    _check_input(x, torch.uint8, "input_tensor")
+    _check_input(wmat, torch.uint8, "weight_tensor")
+    _check_input(y, torch.uint32, "output_tensor")
+    _check_input(lut, torch.uint16, "lut_appmult_tensor")
+    if x.dim() != 4 or wmat.dim() != 2 or y.dim() != 2:
+        raise RuntimeError("input_tensor must be 4-D, weight_tensor and output_tensor 2-D")
+    B, C, H, W = x.shape
+    K, Cout = wmat.shape
+    Ho, Wo = _conv_out(H, W, kh, kw, stride, pad, dil)
+    if K != C * kh * kw:
+        raise RuntimeError(f"weight_tensor's shape should be {C * kh * kw} x Cout")
+    if tuple(y.shape) != (B * Ho * Wo, Cout):
+        raise RuntimeError(f"output_tensor's shape should be {B * Ho * Wo} x {Cout}")
+    bits = _bits_of(lut, "lut_appmult_tensor")
+    if wmat.device != x.device or y.device != x.device or lut.device != x.device:
+        raise RuntimeError("device id not match")
+    with torch.cuda.device(x.device):
+        rc = _load().lutgemm_conv2d_forward(x.data_ptr(), wmat.data_ptr(), y.data_ptr(), lut.data_ptr(), bits, B, C, H,
+                                            W, Cout, kh, kw, stride, pad, dil, _stream_ptr(x.device))
+    _check(rc, "approx_conv2d_forward")
+
+
+def approx_conv2d_backward(gy: torch.Tensor, x: torch.Tensor, wmat: torch.Tensor, gx: torch.Tensor, gw: torch.Tensor,
+                           lut_grad_a: torch.Tensor, lut_grad_b: torch.Tensor, kh: int, kw: int, stride: int, pad: int,
+                           dil: int) -> None:
+    """Fused-im2col convolution backward.  gy: f32 [B*Ho*Wo, Cout]; gx: f32 [B,C,H,W] and gw: f32
+    [C*kh*kw, Cout] are written in place."""
+    _check_input(gy, torch.float32, "grad_output_tensor")
+    _check_input(x, torch.uint8, "input_tensor")
+    _check_input(wmat, torch.uint8, "weight_tensor")
+    _check_input(gx, torch.float32, "grad_input_tensor")
+    _check_input(gw, torch.float32, "grad_weight_tensor")
+    _check_input(lut_grad_a, torch.int16, "lut_grad_a_tensor")
+    _check_input(lut_grad_b, torch.int16, "lut_grad_b_tensor")
+    B, C, H, W = x.shape
+    K, Cout = wmat.shape
+    Ho, Wo = _conv_out(H, W, kh, kw, stride, pad, dil)
+    if K != C * kh * kw or tuple(gy.shape) != (B * Ho * Wo, Cout) or tuple(gx.shape) != tuple(x.shape) \
+            or tuple(gw.shape) != (K, Cout):
+        raise RuntimeError("approx_conv2d_backward: tensor shapes do not match the convolution geometry")
+    bits = _bits_of(lut_grad_a, "lut_grad_a_tensor")
+    if _bits_of(lut_grad_b, "lut_grad_b_tensor") != bits:
+        raise RuntimeError("lut_grad_a_tensor and lut_grad_b_tensor must have the same length")
+    dev = gy.device
+    for t in (x, wmat, gx, gw, lut_grad_a, lut_grad_b):
+        if t.device != dev:
+            raise RuntimeError("All tensors should be on the same device")
+    lib = _load()
+    with torch.cuda.device(dev):
+        nbytes = lib.lutgemm_conv2d_backward_scratch_bytes(bits, B, C, H, W, Cout, kh, kw, stride, pad, dil)
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        rc = lib.lutgemm_conv2d_backward(gy.data_ptr(), x.data_ptr(), wmat.data_ptr(), gx.data_ptr(), gw.data_ptr(),
+                                         lut_grad_a.data_ptr(), lut_grad_b.data_ptr(), bits, B, C, H, W, Cout, kh, kw,
+                                         stride, pad, dil, scratch.data_ptr(), nbytes, _stream_ptr(dev))
+    _check(rc, "approx_conv2d_backward")

@@ -102,31 +102,35 @@ int lutgemm_bits_from_elem_num(long elem_num) {
     return LUTGEMM_E_BITS;
 }
 
-int lutgemm_forward(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K,
-                    int N, void *stream) {
+// ---- shared bodies of the GEMM and the implicit-im2col entry points ------------------------------------
+static int forward_impl(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K,
+                        int N, const lutgemm::ConvGeom &conv, void *stream) {
     if (!lutgemm::bits_supported(bits)) return LUTGEMM_E_BITS;
     if (!a || !w || !c || !lut || M <= 0 || K <= 0 || N <= 0) return LUTGEMM_E_BADARG;
     if ((reinterpret_cast<uintptr_t>(c) & 3) || (reinterpret_cast<uintptr_t>(lut) & 1)) return LUTGEMM_E_BADARG;
     const int sms = current_num_sms();
     if (sms <= 0) return LUTGEMM_E_CUDA;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
     // Large-M problems with reasonably filled 512x64 tiles go to the slab kernel; small or skinny ones
     // to the row-broadcast kernel.  LUTGEMM_FORWARD_KERNEL=rowbcast|slab overrides (for A/B timing).
-    const long tm = (M + 511) / 512, tn = (N + 63) / 64;
-    const double fill = (double)M * N / ((double)tm * 512 * tn * 64);
-    bool slab = M >= 512 && N >= 32 && fill >= 0.6;
-    if (const char *force = getenv("LUTGEMM_FORWARD_KERNEL")) {
-        if (!strcmp(force, "rowbcast")) slab = false;
-        if (!strcmp(force, "slab")) slab = true;
-    }
+    bool slab = M >= 512 && N >= 32 && slab_fill(M, N) >= 0.6;
+    if (env_is("LUTGEMM_FORWARD_KERNEL", "rowbcast")) slab = false;
+    if (env_is("LUTGEMM_FORWARD_KERNEL", "slab")) slab = true;
     if (slab) {
         // Two implementations of the slab algorithm: barrier-synchronous (default: faster on B200 at 7 and
         // 8 bits, 12.8 vs 17.6 ms at 8-bit 4096^3, where four producer warps cannot build slabs fast
-        // enough) and warp-specialised (LUTGEMM_SLAB_IMPL=ws).
-        if (env_is("LUTGEMM_SLAB_IMPL", "ws"))
-            return lutgemm::forward_slab_ws(a, w, c, lut, bits, M, K, N, sms, static_cast<cudaStream_t>(stream));
-        return lutgemm::forward_slab(a, w, c, lut, bits, M, K, N, sms, static_cast<cudaStream_t>(stream));
+        // enough) and warp-specialised (LUTGEMM_SLAB_IMPL=ws, plain GEMM operands only).
+        if (!conv.enabled && env_is("LUTGEMM_SLAB_IMPL", "ws"))
+            return lutgemm::forward_slab_ws(a, w, c, lut, bits, M, K, N, sms, s);
+        return lutgemm::forward_slab(a, w, c, lut, bits, M, K, N, conv, sms, s);
     }
-    return lutgemm::forward_rowbcast(a, w, c, lut, bits, M, K, N, sms, static_cast<cudaStream_t>(stream));
+    return lutgemm::forward_rowbcast(a, w, c, lut, bits, M, K, N, conv, sms, s);
+}
+
+int lutgemm_forward(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K,
+                    int N, void *stream) {
+    lutgemm::ConvGeom none{};
+    return forward_impl(a, w, c, lut, bits, M, K, N, none, stream);
 }
 
 int lutgemm_device_error(int *value) {
@@ -146,9 +150,9 @@ size_t lutgemm_backward_scratch_bytes(int bits, int M, int K, int N) {
     return pl.gw_scratch > pl.ga_scratch ? pl.gw_scratch : pl.ga_scratch;
 }
 
-int lutgemm_backward(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, float *gw,
-                     const int16_t *lut_ga, const int16_t *lut_gw, int bits, int M, int K, int N, void *scratch,
-                     size_t scratch_bytes, void *stream) {
+static int backward_impl(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, float *gw,
+                         const int16_t *lut_ga, const int16_t *lut_gw, int bits, int M, int K, int N,
+                         const lutgemm::ConvGeom &conv, void *scratch, size_t scratch_bytes, void *stream) {
     if (!lutgemm::bits_supported(bits)) return LUTGEMM_E_BITS;
     if (!gc || !a || !w || M <= 0 || K <= 0 || N <= 0) return LUTGEMM_E_BADARG;
     if ((ga && !lut_ga) || (gw && !lut_gw)) return LUTGEMM_E_BADARG;
@@ -161,23 +165,79 @@ int lutgemm_backward(const float *gc, const uint8_t *a, const uint8_t *w, float 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const BackwardPlan pl = plan_backward(bits, M, K, N, sms);
     float *sc = static_cast<float *>(scratch);
+    const bool ws_impl = !conv.enabled && env_is("LUTGEMM_SLAB_IMPL", "ws");
     if (gw) {
         // the weight gradient goes first: under data parallelism its all-reduce can then overlap gA
         if (pl.gw_scratch && (!scratch || scratch_bytes < pl.gw_scratch)) return LUTGEMM_E_SCRATCH;
-        const bool sync_impl = !env_is("LUTGEMM_SLAB_IMPL", "ws");
-        int rc = !pl.gw_slab ? lutgemm::backward_gw(gc, a, w, gw, lut_gw, bits, M, K, N, sc, pl.gw_splits, sms, s)
-                 : sync_impl ? lutgemm::backward_gw_slab(gc, a, w, gw, lut_gw, bits, M, K, N, sc, sms, s)
-                             : lutgemm::backward_gw_slab_ws(gc, a, w, gw, lut_gw, bits, M, K, N, sc, sms, s);
+        int rc = !pl.gw_slab ? lutgemm::backward_gw(gc, a, w, gw, lut_gw, bits, M, K, N, conv, sc, pl.gw_splits, sms, s)
+                 : ws_impl   ? lutgemm::backward_gw_slab_ws(gc, a, w, gw, lut_gw, bits, M, K, N, sc, sms, s)
+                             : lutgemm::backward_gw_slab(gc, a, w, gw, lut_gw, bits, M, K, N, conv, sc, sms, s);
         if (rc != LUTGEMM_OK) return rc;
     }
     if (ga) {
         if (pl.ga_scratch && (!scratch || scratch_bytes < pl.ga_scratch)) return LUTGEMM_E_SCRATCH;
-        const bool sync_impl = !env_is("LUTGEMM_SLAB_IMPL", "ws");
-        int rc = !pl.ga_slab ? lutgemm::backward_ga(gc, a, w, ga, lut_ga, bits, M, K, N, sms, s)
-                 : sync_impl ? lutgemm::backward_ga_slab(gc, a, w, ga, lut_ga, bits, M, K, N, sc, sms, s)
-                             : lutgemm::backward_ga_slab_ws(gc, a, w, ga, lut_ga, bits, M, K, N, sc, sms, s);
+        int rc = !pl.ga_slab ? lutgemm::backward_ga(gc, a, w, ga, lut_ga, bits, M, K, N, conv, sms, s)
+                 : ws_impl   ? lutgemm::backward_ga_slab_ws(gc, a, w, ga, lut_ga, bits, M, K, N, sc, sms, s)
+                             : lutgemm::backward_ga_slab(gc, a, w, ga, lut_ga, bits, M, K, N, conv, sc, sms, s);
         if (rc != LUTGEMM_OK) return rc;
     }
+    return LUTGEMM_OK;
+}
+
+int lutgemm_backward(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, float *gw,
+                     const int16_t *lut_ga, const int16_t *lut_gw, int bits, int M, int K, int N, void *scratch,
+                     size_t scratch_bytes, void *stream) {
+    lutgemm::ConvGeom none{};
+    return backward_impl(gc, a, w, ga, gw, lut_ga, lut_gw, bits, M, K, N, none, scratch, scratch_bytes, stream);
+}
+
+// ---- convolution entry points (implicit im2col) ------------------------------------------------------------
+static int make_geom(int B, int C, int H, int W, int kh, int kw, int stride, int pad, int dil, lutgemm::ConvGeom *g) {
+    if (B <= 0 || C <= 0 || H <= 0 || W <= 0 || kh <= 0 || kw <= 0 || stride <= 0 || pad < 0 || dil <= 0)
+        return LUTGEMM_E_BADARG;
+    const long Ho = ((long)H + 2L * pad - (long)dil * (kh - 1) - 1) / stride + 1;
+    const long Wo = ((long)W + 2L * pad - (long)dil * (kw - 1) - 1) / stride + 1;
+    if (Ho <= 0 || Wo <= 0) return LUTGEMM_E_BADARG;
+    if ((long)B * Ho * Wo > 0x7fffffffL || (long)C * kh * kw > 0x7fffffffL) return LUTGEMM_E_TOOLARGE;
+    g->enabled = 1; g->B = B; g->C = C; g->H = H; g->W = W; g->kh = kh; g->kw = kw;
+    g->stride = stride; g->pad = pad; g->dil = dil; g->Ho = (int)Ho; g->Wo = (int)Wo;
+    return LUTGEMM_OK;
+}
+
+int lutgemm_conv2d_forward(const uint8_t *x, const uint8_t *wmat, uint32_t *y, const uint16_t *lut, int bits, int B,
+                           int C, int H, int W, int Cout, int kh, int kw, int stride, int pad, int dil,
+                           void *stream) {
+    lutgemm::ConvGeom g{};
+    const int rc = make_geom(B, C, H, W, kh, kw, stride, pad, dil, &g);
+    if (rc != LUTGEMM_OK) return rc;
+    return forward_impl(x, wmat, y, lut, bits, B * g.Ho * g.Wo, C * kh * kw, Cout, g, stream);
+}
+
+size_t lutgemm_conv2d_backward_scratch_bytes(int bits, int B, int C, int H, int W, int Cout, int kh, int kw,
+                                             int stride, int pad, int dil) {
+    lutgemm::ConvGeom g{};
+    if (make_geom(B, C, H, W, kh, kw, stride, pad, dil, &g) != LUTGEMM_OK) return 0;
+    const size_t M = (size_t)B * g.Ho * g.Wo, K = (size_t)C * kh * kw;
+    // the unfolded activation gradient [B][K][Ho*Wo], then what the two gradient kernels need
+    return M * K * sizeof(float) + lutgemm_backward_scratch_bytes(bits, (int)M, (int)K, Cout);
+}
+
+int lutgemm_conv2d_backward(const float *gy, const uint8_t *x, const uint8_t *wmat, float *gx, float *gw,
+                            const int16_t *lut_ga, const int16_t *lut_gw, int bits, int B, int C, int H, int W,
+                            int Cout, int kh, int kw, int stride, int pad, int dil, void *scratch,
+                            size_t scratch_bytes, void *stream) {
+    lutgemm::ConvGeom g{};
+    int rc = make_geom(B, C, H, W, kh, kw, stride, pad, dil, &g);
+    if (rc != LUTGEMM_OK) return rc;
+    const int M = B * g.Ho * g.Wo, K = C * kh * kw;
+    const size_t col_bytes = gx ? (size_t)M * K * sizeof(float) : 0;
+    if (gx && (!scratch || scratch_bytes < col_bytes)) return LUTGEMM_E_SCRATCH;
+    float *gcol = static_cast<float *>(scratch);
+    void *rest = scratch ? static_cast<char *>(scratch) + col_bytes : nullptr;
+    const size_t rest_bytes = scratch_bytes > col_bytes ? scratch_bytes - col_bytes : 0;
+    rc = backward_impl(gy, x, wmat, gx ? gcol : nullptr, gw, lut_ga, lut_gw, bits, M, K, Cout, g, rest, rest_bytes, stream);
+    if (rc != LUTGEMM_OK) return rc;
+    if (gx) return lutgemm::col2im_gather(gcol, gx, g, static_cast<cudaStream_t>(stream));
     return LUTGEMM_OK;
 }
 

@@ -40,7 +40,7 @@ template <int BITS, int R, int C, int WM, int WK>
 __global__ void __launch_bounds__(32 * WM * WK, 1)
 ga_colbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, const uint8_t *__restrict__ w,
                    float *__restrict__ ga, const int16_t *__restrict__ lut, int M, int K, int N, int tiles_m,
-                   int tiles_k, int vec_g, int vec_w, int vec_o) {
+                   int tiles_k, int vec_g, int vec_w, int vec_o, const ConvGeom conv) {
     using Cfg = GaCfg<BITS, R, C, WM, WK>;
     constexpr int MT = Cfg::MT, KT = Cfg::KT, NT = Cfg::NT, GS = Cfg::GSTRIDE, THREADS = Cfg::THREADS;
     constexpr uint32_t MASK = Cfg::Q - 1;
@@ -105,7 +105,7 @@ ga_colbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, 
 #pragma unroll
             for (int i = 0; i < R; ++i) {
                 const int k = kth + i;
-                uint32_t code = (m < M && k < K) ? a[(size_t)m * K + k] : 0u;
+                uint32_t code = !(m < M && k < K) ? 0u : conv.enabled ? conv_code(a, conv, m, k) : a[(size_t)m * K + k];
                 aoff[i][j] = (code & MASK) * 2u;
                 acc[i][j] = 0.f;
             }
@@ -145,6 +145,16 @@ ga_colbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, 
         for (int j = 0; j < C; ++j) {
             const int m = mth + 32 * j;
             if (m >= M) continue;
+            if (conv.enabled) {
+                // [B][K][L] layout (what col2im consumes): consecutive lanes are consecutive l, so each of
+                // these scalar stores is coalesced across the warp
+                const int L = conv.Ho * conv.Wo, b = m / L;
+                float *obase = ga + ((size_t)b * K + kth) * L + (m - b * L);
+#pragma unroll
+                for (int i = 0; i < R; ++i)
+                    if (kth + i < K) obase[(size_t)i * L] = acc[i][j] * kGradFactor;
+                continue;
+            }
             float *orow = ga + (size_t)m * K + kth;
             if (vec_o) {
 #pragma unroll
@@ -165,7 +175,7 @@ ga_colbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, 
 
 template <int BITS, int R, int C, int WM, int WK>
 static int launch_ga(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, const int16_t *lut, int M,
-                     int K, int N, int num_sms, cudaStream_t stream) {
+                     int K, int N, const ConvGeom &conv, int num_sms, cudaStream_t stream) {
     using Cfg = GaCfg<BITS, R, C, WM, WK>;
     auto kern = ga_colbcast_kernel<BITS, R, C, WM, WK>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess)
@@ -177,17 +187,18 @@ static int launch_ga(const float *gc, const uint8_t *a, const uint8_t *w, float 
     const int vec_g = (N % 4 == 0) && ((reinterpret_cast<uintptr_t>(gc) & 15) == 0);
     const int vec_w = (N % 16 == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
     const int vec_o = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(ga) & 15) == 0);
-    kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(gc, a, w, ga, lut, M, K, N, tiles_m, tiles_k, vec_g, vec_w, vec_o);
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(gc, a, w, ga, lut, M, K, N, tiles_m, tiles_k, vec_g, vec_w, vec_o,
+                                                    conv);
     return cudaGetLastError() == cudaSuccess ? LUTGEMM_OK : LUTGEMM_E_CUDA;
 }
 
 int backward_ga(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, const int16_t *lut_ga, int bits,
-                int M, int K, int N, int num_sms, cudaStream_t stream) {
+                int M, int K, int N, const ConvGeom &conv, int num_sms, cudaStream_t stream) {
     switch (bits) {
-        case 4: return launch_ga<4, 8, 4, 2, 4>(gc, a, w, ga, lut_ga, M, K, N, num_sms, stream);
-        case 6: return launch_ga<6, 8, 4, 2, 4>(gc, a, w, ga, lut_ga, M, K, N, num_sms, stream);
-        case 7: return launch_ga<7, 8, 4, 2, 4>(gc, a, w, ga, lut_ga, M, K, N, num_sms, stream);
-        case 8: return launch_ga<8, 8, 4, 2, 4>(gc, a, w, ga, lut_ga, M, K, N, num_sms, stream);
+        case 4: return launch_ga<4, 8, 4, 2, 4>(gc, a, w, ga, lut_ga, M, K, N, conv, num_sms, stream);
+        case 6: return launch_ga<6, 8, 4, 2, 4>(gc, a, w, ga, lut_ga, M, K, N, conv, num_sms, stream);
+        case 7: return launch_ga<7, 8, 4, 2, 4>(gc, a, w, ga, lut_ga, M, K, N, conv, num_sms, stream);
+        case 8: return launch_ga<8, 8, 4, 2, 4>(gc, a, w, ga, lut_ga, M, K, N, conv, num_sms, stream);
     }
     return LUTGEMM_E_BITS;
 }
@@ -215,7 +226,8 @@ template <int BITS, int R, int C, int WK, int WN>
 __global__ void __launch_bounds__(32 * WK * WN, 1)
 gw_rowbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, const uint8_t *__restrict__ w,
                    float *__restrict__ out, const int16_t *__restrict__ lut, int M, int K, int N, int tiles_k,
-                   int tiles_n, int num_splits, int rows_per_split, float out_scale, int vec_a, int vec_g) {
+                   int tiles_n, int num_splits, int rows_per_split, float out_scale, int vec_a, int vec_g,
+                   const ConvGeom conv) {
     using Cfg = GwCfg<BITS, R, C, WK, WN>;
     constexpr int MT = Cfg::MT, KT = Cfg::KT, NT = Cfg::NT, THREADS = Cfg::THREADS;
     constexpr uint32_t MASK = Cfg::Q - 1;
@@ -247,7 +259,9 @@ gw_rowbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, 
             for (int id = tid; id < MT * KT; id += THREADS) {
                 int r = id / KT, kk = id % KT;
                 int gm = mbase + r, gk = k0 + kk;
-                as[id] = (gm < mend && gk < K) ? a[(size_t)gm * K + gk] : (uint8_t)0;
+                as[id] = !(gm < mend && gk < K) ? (uint8_t)0
+                         : conv.enabled          ? (uint8_t)conv_code(a, conv, gm, gk)
+                                                 : a[(size_t)gm * K + gk];
             }
         }
         if (vec_g) {
@@ -368,7 +382,8 @@ int gw_num_splits(int bits, int M, int K, int N, int num_sms) {
 
 template <int BITS, int R, int C, int WK, int WN>
 static int launch_gw(const float *gc, const uint8_t *a, const uint8_t *w, float *gw, const int16_t *lut, int M,
-                     int K, int N, float *scratch, int num_splits, int num_sms, cudaStream_t stream) {
+                     int K, int N, const ConvGeom &conv, float *scratch, int num_splits, int num_sms,
+                     cudaStream_t stream) {
     using Cfg = GwCfg<BITS, R, C, WK, WN>;
     auto kern = gw_rowbcast_kernel<BITS, R, C, WK, WN>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess)
@@ -379,12 +394,12 @@ static int launch_gw(const float *gc, const uint8_t *a, const uint8_t *w, float 
     const int grid = (int)(items < (long)num_sms * ctas_per_sm ? items : (long)num_sms * ctas_per_sm);
     int rows_per_split = (M + num_splits - 1) / num_splits;
     rows_per_split = (rows_per_split + Cfg::MT - 1) / Cfg::MT * Cfg::MT;
-    const int vec_a = (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(a) & 15) == 0);
+    const int vec_a = !conv.enabled && (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(a) & 15) == 0);
     const int vec_g = (N % 4 == 0) && ((reinterpret_cast<uintptr_t>(gc) & 15) == 0);
     float *out = num_splits > 1 ? scratch : gw;
     const float scale = num_splits > 1 ? 1.0f : kGradFactor;
     kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(gc, a, w, out, lut, M, K, N, tiles_k, tiles_n, num_splits,
-                                                    rows_per_split, scale, vec_a, vec_g);
+                                                    rows_per_split, scale, vec_a, vec_g, conv);
     if (cudaGetLastError() != cudaSuccess) return LUTGEMM_E_CUDA;
     if (num_splits > 1) {
         const long KN = (long)K * N;
@@ -397,23 +412,66 @@ static int launch_gw(const float *gc, const uint8_t *a, const uint8_t *w, float 
 
 template <int BITS>
 static int dispatch_gw(const float *gc, const uint8_t *a, const uint8_t *w, float *gw, const int16_t *lut, int M,
-                       int K, int N, float *scratch, int num_splits, int num_sms, cudaStream_t stream) {
+                       int K, int N, const ConvGeom &conv, float *scratch, int num_splits, int num_sms,
+                       cudaStream_t stream) {
     if (gw_use_narrow(N))
-        return launch_gw<BITS, kGwNarrowR, kGwNarrowC, kGwWarps, 1>(gc, a, w, gw, lut, M, K, N, scratch, num_splits,
-                                                                     num_sms, stream);
-    return launch_gw<BITS, kGwWideR, kGwWideC, kGwWarps, 1>(gc, a, w, gw, lut, M, K, N, scratch, num_splits, num_sms,
-                                                             stream);
+        return launch_gw<BITS, kGwNarrowR, kGwNarrowC, kGwWarps, 1>(gc, a, w, gw, lut, M, K, N, conv, scratch,
+                                                                     num_splits, num_sms, stream);
+    return launch_gw<BITS, kGwWideR, kGwWideC, kGwWarps, 1>(gc, a, w, gw, lut, M, K, N, conv, scratch, num_splits,
+                                                             num_sms, stream);
 }
 
 int backward_gw(const float *gc, const uint8_t *a, const uint8_t *w, float *gw, const int16_t *lut_gw, int bits,
-                int M, int K, int N, float *scratch, int num_splits, int num_sms, cudaStream_t stream) {
+                int M, int K, int N, const ConvGeom &conv, float *scratch, int num_splits, int num_sms,
+                cudaStream_t stream) {
     switch (bits) {
-        case 4: return dispatch_gw<4>(gc, a, w, gw, lut_gw, M, K, N, scratch, num_splits, num_sms, stream);
-        case 6: return dispatch_gw<6>(gc, a, w, gw, lut_gw, M, K, N, scratch, num_splits, num_sms, stream);
-        case 7: return dispatch_gw<7>(gc, a, w, gw, lut_gw, M, K, N, scratch, num_splits, num_sms, stream);
-        case 8: return dispatch_gw<8>(gc, a, w, gw, lut_gw, M, K, N, scratch, num_splits, num_sms, stream);
+        case 4: return dispatch_gw<4>(gc, a, w, gw, lut_gw, M, K, N, conv, scratch, num_splits, num_sms, stream);
+        case 6: return dispatch_gw<6>(gc, a, w, gw, lut_gw, M, K, N, conv, scratch, num_splits, num_sms, stream);
+        case 7: return dispatch_gw<7>(gc, a, w, gw, lut_gw, M, K, N, conv, scratch, num_splits, num_sms, stream);
+        case 8: return dispatch_gw<8>(gc, a, w, gw, lut_gw, M, K, N, conv, scratch, num_splits, num_sms, stream);
     }
     return LUTGEMM_E_BITS;
+}
+
+// ------------------------------------------------------------------------------------------------
+// col2im: gx[b,c,h,w] = sum over the taps (i, j) that reach (h, w) of gcol[b][(c*kh+i)*kw+j][oh*Wo+ow].
+// A gather (one thread per input pixel, taps in ascending (i, j) order), so the fp32 sum order is fixed;
+// consecutive threads read consecutive ow of the same gcol row.  Adjoint of the implicit im2col above
+// (the reference gets it from autograd of F.unfold / F.pad, self_ops/ops_py/approx_ops.py:556-563).
+// ------------------------------------------------------------------------------------------------
+__global__ void col2im_gather_kernel(const float *__restrict__ gcol, float *__restrict__ gx, const ConvGeom g) {
+    const long total = (long)g.B * g.C * g.H * g.W;
+    const int L = g.Ho * g.Wo, K = g.C * g.kh * g.kw;
+    for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
+        const int w = (int)(idx % g.W);
+        const int h = (int)((idx / g.W) % g.H);
+        const int c = (int)((idx / ((long)g.W * g.H)) % g.C);
+        const int b = (int)(idx / ((long)g.W * g.H * g.C));
+        const float *base = gcol + ((size_t)b * K + (size_t)c * g.kh * g.kw) * L;
+        float s = 0.f;
+        for (int i = 0; i < g.kh; ++i) {
+            const int th = h + g.pad - i * g.dil;
+            if (th < 0 || th % g.stride) continue;
+            const int oh = th / g.stride;
+            if (oh >= g.Ho) continue;
+            for (int j = 0; j < g.kw; ++j) {
+                const int tw = w + g.pad - j * g.dil;
+                if (tw < 0 || tw % g.stride) continue;
+                const int ow = tw / g.stride;
+                if (ow >= g.Wo) continue;
+                s += base[(size_t)(i * g.kw + j) * L + oh * g.Wo + ow];
+            }
+        }
+        gx[idx] = s;
+    }
+}
+
+int col2im_gather(const float *gcol, float *gx, const ConvGeom &g, cudaStream_t stream) {
+    const long total = (long)g.B * g.C * g.H * g.W;
+    const long blocks = (total + 255) / 256;
+    const int grid = (int)(blocks < 148L * 16 ? blocks : 148L * 16);
+    col2im_gather_kernel<<<grid, 256, 0, stream>>>(gcol, gx, g);
+    return cudaGetLastError() == cudaSuccess ? LUTGEMM_OK : LUTGEMM_E_CUDA;
 }
 
 }  // namespace lutgemm

@@ -21,6 +21,44 @@ constexpr float kGradFactor = 1.0f / 16.0f;  // approx_mult.h:41
 
 inline bool bits_supported(int bits) { return bits == 4 || bits == 6 || bits == 7 || bits == 8; }
 
+// ---- implicit im2col ---------------------------------------------------------------------------
+// Geometry of a convolution whose unfolded activation matrix a[m,k] is never materialised:
+//   m = (b*Ho + oh)*Wo + ow,  k = (c*kh + i)*kw + j,  a[m,k] = x[b,c,oh*stride-pad+i*dil,ow*stride-pad+j*dil]
+// or code 0 outside the image (the reference pads the code tensor with 0 before unfolding,
+// self_ops/ops_py/approx_ops.py:556-563, so padding looks up LUT[0][w]).
+struct ConvGeom {
+    int enabled;
+    int B, C, H, W, kh, kw, stride, pad, dil, Ho, Wo;
+};
+
+__device__ __forceinline__ uint32_t conv_code(const uint8_t *__restrict__ x, const ConvGeom &g, int m, int k) {
+    const int L = g.Ho * g.Wo, kk = g.kh * g.kw;
+    const int b = m / L, l = m - b * L, oh = l / g.Wo, ow = l - oh * g.Wo;
+    const int c = k / kk, r = k - c * kk, i = r / g.kw, j = r - i * g.kw;
+    const int ih = oh * g.stride - g.pad + i * g.dil, iw = ow * g.stride - g.pad + j * g.dil;
+    if ((unsigned)ih < (unsigned)g.H && (unsigned)iw < (unsigned)g.W)
+        return x[((size_t)(b * g.C + c) * g.H + ih) * g.W + iw];
+    return 0u;
+}
+
+// 16 consecutive k of one unfolded row, packed little-endian into four words (k >= K gives 0)
+__device__ __forceinline__ uint4 conv_code16(const uint8_t *__restrict__ x, const ConvGeom &g, int m, int kbase, int K) {
+    const int L = g.Ho * g.Wo, kk = g.kh * g.kw;
+    const int b = m / L, l = m - b * L, oh = l / g.Wo, ow = l - oh * g.Wo;
+    int c = kbase / kk, r = kbase - c * kk, i = r / g.kw, j = r - i * g.kw;
+    const int ih0 = oh * g.stride - g.pad, iw0 = ow * g.stride - g.pad;
+    const uint8_t *xb = x + (size_t)b * g.C * g.H * g.W;
+    uint32_t t[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int q = 0; q < 16; ++q) {
+        const int ih = ih0 + i * g.dil, iw = iw0 + j * g.dil;
+        if (kbase + q < K && (unsigned)ih < (unsigned)g.H && (unsigned)iw < (unsigned)g.W)
+            t[q >> 2] |= (uint32_t)xb[((size_t)c * g.H + ih) * g.W + iw] << (8 * (q & 3));
+        if (++j == g.kw) { j = 0; if (++i == g.kh) { i = 0; ++c; } }
+    }
+    return make_uint4(t[0], t[1], t[2], t[3]);
+}
+
 // ---- small device helpers ----------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

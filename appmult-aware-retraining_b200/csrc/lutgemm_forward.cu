@@ -31,7 +31,7 @@ template <int BITS, int R, int C, int WM, int WN>
 __global__ void __launch_bounds__(32 * WM * WN, 1)
 fwd_rowbcast_kernel(const uint8_t *__restrict__ a, const uint8_t *__restrict__ w, uint32_t *__restrict__ c,
                     const uint16_t *__restrict__ lut, int M, int K, int N, int tiles_m, int tiles_n,
-                    int vec_a, int vec_w, int vec_c) {
+                    int vec_a, int vec_w, int vec_c, const ConvGeom conv) {
     using Cfg = FwdCfg<BITS, R, C, WM, WN>;
     constexpr int KT = Cfg::KT, MT = Cfg::MT, NT = Cfg::NT, THREADS = Cfg::THREADS;
     constexpr uint32_t MASK = Cfg::Q - 1;
@@ -66,7 +66,7 @@ fwd_rowbcast_kernel(const uint8_t *__restrict__ a, const uint8_t *__restrict__ w
             for (int id = tid; id < MT * KT; id += THREADS) {
                 int r = id / KT, kk = id % KT;
                 int gm = min(m0 + r, M - 1), gk = kbase + kk;
-                as[id] = gk < K ? a[(size_t)gm * K + gk] : (uint8_t)0;
+                as[id] = gk >= K ? (uint8_t)0 : conv.enabled ? (uint8_t)conv_code(a, conv, gm, gk) : a[(size_t)gm * K + gk];
             }
         }
         if (vec_w) {
@@ -186,7 +186,7 @@ fwd_rowbcast_kernel(const uint8_t *__restrict__ a, const uint8_t *__restrict__ w
 
 template <int BITS, int R, int C, int WM, int WN>
 static int launch_fwd(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int M, int K, int N,
-                      int num_sms, cudaStream_t stream) {
+                      const ConvGeom &conv, int num_sms, cudaStream_t stream) {
     using Cfg = FwdCfg<BITS, R, C, WM, WN>;
     auto kern = fwd_rowbcast_kernel<BITS, R, C, WM, WN>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
@@ -195,27 +195,27 @@ static int launch_fwd(const uint8_t *a, const uint8_t *w, uint32_t *c, const uin
     const long tiles = (long)tiles_m * tiles_n;
     const int ctas_per_sm = Cfg::SMEM <= 100 * 1024 ? 2 : 1;
     const int grid = (int)(tiles < (long)num_sms * ctas_per_sm ? tiles : (long)num_sms * ctas_per_sm);
-    const int vec_a = (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(a) & 15) == 0);
+    const int vec_a = !conv.enabled && (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(a) & 15) == 0);
     const int vec_w = (N % 16 == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
     const int vec_c = (N % 4 == 0) && ((reinterpret_cast<uintptr_t>(c) & 15) == 0);
-    kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(a, w, c, lut, M, K, N, tiles_m, tiles_n, vec_a, vec_w, vec_c);
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(a, w, c, lut, M, K, N, tiles_m, tiles_n, vec_a, vec_w, vec_c, conv);
     return cudaGetLastError() == cudaSuccess ? LUTGEMM_OK : LUTGEMM_E_CUDA;
 }
 
 template <int BITS>
 static int dispatch_fwd(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int M, int K, int N,
-                        int num_sms, cudaStream_t stream) {
-    if (N <= 128) return launch_fwd<BITS, 16, 2, 8, 1>(a, w, c, lut, M, K, N, num_sms, stream);
-    return launch_fwd<BITS, 8, 8, 8, 1>(a, w, c, lut, M, K, N, num_sms, stream);
+                        const ConvGeom &conv, int num_sms, cudaStream_t stream) {
+    if (N <= 128) return launch_fwd<BITS, 16, 2, 8, 1>(a, w, c, lut, M, K, N, conv, num_sms, stream);
+    return launch_fwd<BITS, 8, 8, 8, 1>(a, w, c, lut, M, K, N, conv, num_sms, stream);
 }
 
 int forward_rowbcast(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K,
-                     int N, int num_sms, cudaStream_t stream) {
+                     int N, const ConvGeom &conv, int num_sms, cudaStream_t stream) {
     switch (bits) {
-        case 4: return dispatch_fwd<4>(a, w, c, lut, M, K, N, num_sms, stream);
-        case 6: return dispatch_fwd<6>(a, w, c, lut, M, K, N, num_sms, stream);
-        case 7: return dispatch_fwd<7>(a, w, c, lut, M, K, N, num_sms, stream);
-        case 8: return dispatch_fwd<8>(a, w, c, lut, M, K, N, num_sms, stream);
+        case 4: return dispatch_fwd<4>(a, w, c, lut, M, K, N, conv, num_sms, stream);
+        case 6: return dispatch_fwd<6>(a, w, c, lut, M, K, N, conv, num_sms, stream);
+        case 7: return dispatch_fwd<7>(a, w, c, lut, M, K, N, conv, num_sms, stream);
+        case 8: return dispatch_fwd<8>(a, w, c, lut, M, K, N, conv, num_sms, stream);
     }
     return LUTGEMM_E_BITS;
 }

@@ -7,16 +7,18 @@
 
 namespace lutgemm {
 
+struct ConvGeom;  // lutgemm_common.cuh; geometry.enabled == 0 means `a` is a plain [M,K] matrix
+
 int forward_rowbcast(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K,
-                     int N, int num_sms, cudaStream_t stream);
+                     int N, const ConvGeom &conv, int num_sms, cudaStream_t stream);
 
 int forward_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K, int N,
-                 int num_sms, cudaStream_t stream);
+                 const ConvGeom &conv, int num_sms, cudaStream_t stream);
 
 int backward_gw_slab(const float *gc, const uint8_t *a, const uint8_t *w, float *gw, const int16_t *lut_gw, int bits,
-                     int M, int K, int N, float *scratch, int num_sms, cudaStream_t stream);
+                     int M, int K, int N, const ConvGeom &conv, float *scratch, int num_sms, cudaStream_t stream);
 int backward_ga_slab(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, const int16_t *lut_ga, int bits,
-                     int M, int K, int N, float *scratch, int num_sms, cudaStream_t stream);
+                     int M, int K, int N, const ConvGeom &conv, float *scratch, int num_sms, cudaStream_t stream);
 // warp-specialised variants of the three slab kernels (producer warps build slabs, consumer warps gather)
 int forward_slab_ws(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K,
                     int N, int num_sms, cudaStream_t stream);
@@ -29,19 +31,23 @@ int slab_ws_read_and_clear_error(int *value);
 // launches a one-warp kernel whose barrier wait can never be satisfied (it must time out with error id 99)
 int slab_ws_bounded_wait_selftest(cudaStream_t stream);
 // out[k][c] (or out[c][k] when transpose) = 1/16 * sum over row blocks of part[b][k][c], b ascending
-int slab_reduce_blocks(const float *part, float *out, int K, int C, int nblocks, bool transpose, int num_sms,
-                       cudaStream_t stream);
+int slab_reduce_blocks(const float *part, float *out, int K, int C, int nblocks, bool transpose, int bkl_L,
+                       int num_sms, cudaStream_t stream);
 
 // number of 512-row blocks the slab gradient kernels cut their reduction dimension into
 int slab_grad_row_blocks(int rdim);
+
+// gx[B,C,H,W] from the unfolded activation gradient gcol[B][C*kh*kw][Ho*Wo] (deterministic gather)
+int col2im_gather(const float *gcol, float *gx, const ConvGeom &g, cudaStream_t stream);
 
 // number of slabs the weight-gradient kernel splits M into (1 = no scratch needed)
 int gw_num_splits(int bits, int M, int K, int N, int num_sms);
 
 int backward_ga(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, const int16_t *lut_ga, int bits,
-                int M, int K, int N, int num_sms, cudaStream_t stream);
+                int M, int K, int N, const ConvGeom &conv, int num_sms, cudaStream_t stream);
 
 int backward_gw(const float *gc, const uint8_t *a, const uint8_t *w, float *gw, const int16_t *lut_gw, int bits,
-                int M, int K, int N, float *scratch, int num_splits, int num_sms, cudaStream_t stream);
+                int M, int K, int N, const ConvGeom &conv, float *scratch, int num_splits, int num_sms,
+                cudaStream_t stream);
 
 }  // namespace lutgemm

@@ -70,6 +70,8 @@ struct SlabArgs {
     // on the FMA pipe (the integer ALU pipe is the scarcer one in the use phase)
     uint32_t c_row_bytes;  // U_STRIDE * 4
     uint32_t c_64k;        // 65536
+    ConvGeom conv;         // enabled: `a` is the image-code tensor x[B,C,H,W] and a[m,k] is gathered on the fly
+    int ga_bkl;            // grad_a output layout: 0 = [M][K], 1 = [B][K][Ho*Wo] (what col2im consumes)
 };
 
 // ACC (forward): 0 = two dp2a per word; 1 = full-word add plus shifted add, fixed up at the end;
@@ -111,6 +113,13 @@ __global__ void __launch_bounds__(512, 1) slab_kernel(const SlabArgs p) {
     const uint32_t tt_addr = smem_u32(tt_s);
     const uint32_t u_addr = smem_u32(u_s);
 
+    // position of grad_a element (m, k) in the output: [M][K], or [B][K][L] with m = b*L + l
+    auto ga_index = [&](int m, int k) -> size_t {
+        if (!p.ga_bkl) return (size_t)m * K + k;
+        const int L = p.conv.Ho * p.conv.Wo, b = m / L;
+        return ((size_t)b * K + k) * L + (m - b * L);
+    };
+
     // ---- operand chunk staging: rc_s[stage][kk][r] (512 row codes per k), cc_s[stage][kk][c] (64) ----
     uint4 prc = make_uint4(0, 0, 0, 0), pcc = make_uint4(0, 0, 0, 0);
 
@@ -119,7 +128,9 @@ __global__ void __launch_bounds__(512, 1) slab_kernel(const SlabArgs p) {
         if (MODE != kGa) {
             // row codes a[r][kbase..+15]: one row per thread, transposed when stored
             const uint8_t *src = p.a + (size_t)min(r0 + tid, M - 1) * K + kbase;
-            if (p.vec_a) {
+            if (p.conv.enabled) {
+                prc = conv_code16(p.a, p.conv, min(r0 + tid, M - 1), kbase, K);
+            } else if (p.vec_a) {
                 prc = kbase < K ? *reinterpret_cast<const uint4 *>(src) : make_uint4(0, 0, 0, 0);
             } else {
                 uint32_t t[4] = {0, 0, 0, 0};
@@ -166,7 +177,9 @@ __global__ void __launch_bounds__(512, 1) slab_kernel(const SlabArgs p) {
             // column codes a[c0+c][kbase..+15]: one m-row per thread (64 threads), transposed when stored
             if (tid < CT) {
                 const uint8_t *src = p.a + (size_t)min(c0 + tid, M - 1) * K + kbase;
-                if (p.vec_a) {
+                if (p.conv.enabled) {
+                    pcc = conv_code16(p.a, p.conv, min(c0 + tid, M - 1), kbase, K);
+                } else if (p.vec_a) {
                     pcc = kbase < K ? *reinterpret_cast<const uint4 *>(src) : make_uint4(0, 0, 0, 0);
                 } else {
                     uint32_t t[4] = {0, 0, 0, 0};
@@ -307,7 +320,7 @@ __global__ void __launch_bounds__(512, 1) slab_kernel(const SlabArgs p) {
                 v += __shfl_xor_sync(0xffffffffu, v, 8);
                 v += __shfl_xor_sync(0xffffffffu, v, 16);
                 if (lane < 4 && c0 + col < CDIM) {
-                    if (p.direct && MODE == kGa) obase[(size_t)(c0 + col) * K + (k - 1)] = v * kGradFactor;
+                    if (p.direct && MODE == kGa) obase[ga_index(c0 + col, k - 1)] = v * kGradFactor;
                     else obase[(size_t)(k - 1) * CDIM + c0 + col] = p.direct ? v * kGradFactor : v;
                 }
             }
@@ -395,17 +408,18 @@ __global__ void __launch_bounds__(512, 1) slab_kernel(const SlabArgs p) {
             v += __shfl_xor_sync(0xffffffffu, v, 8);
             v += __shfl_xor_sync(0xffffffffu, v, 16);
             if (lane < 4 && c0 + col < CDIM) {
-                if (p.direct && MODE == kGa) obase[(size_t)(c0 + col) * K + k] = v * kGradFactor;
+                if (p.direct && MODE == kGa) obase[ga_index(c0 + col, k)] = v * kGradFactor;
                 else obase[(size_t)k * CDIM + c0 + col] = p.direct ? v * kGradFactor : v;
             }
         }
     }
 }
 
-// out[k][c] (TRANSPOSE=false) or out[c][k] (TRANSPOSE=true) = scale * sum_b part[b][k][c], b ascending
+// out[k][c] (TRANSPOSE=false) or out[c][k] (TRANSPOSE=true) = scale * sum_b part[b][k][c], b ascending.
+// With bkl_L > 0 (and TRANSPOSE=false) column c = b*L + l goes to out[(b*K + k)*L + l] instead.
 template <bool TRANSPOSE>
 __global__ void slab_reduce_blocks_kernel(const float *__restrict__ part, float *__restrict__ out, int K, int C,
-                                          int nblocks, float scale) {
+                                          int nblocks, float scale, int bkl_L) {
     __shared__ float tile[32][33];
     const int tiles_c = (C + 31) / 32, tiles_k = (K + 31) / 32;
     const size_t KC_ = (size_t)K * C;
@@ -419,7 +433,10 @@ __global__ void slab_reduce_blocks_kernel(const float *__restrict__ part, float 
             if (k < K && c < C)
                 for (int b = 0; b < nblocks; ++b) s += part[(size_t)b * KC_ + (size_t)k * C + c];
             if (TRANSPOSE) tile[ty + 8 * j][tx] = s * scale;
-            else if (k < K && c < C) out[(size_t)k * C + c] = s * scale;
+            else if (k < K && c < C) {
+                if (bkl_L > 0) out[((size_t)(c / bkl_L) * K + k) * bkl_L + c % bkl_L] = s * scale;
+                else out[(size_t)k * C + c] = s * scale;
+            }
         }
         if (TRANSPOSE) {
             __syncthreads();
@@ -443,13 +460,14 @@ static int env_int(const char *name, int dflt) {
 
 template <int BITS, int ACC>
 static int launch_fwd_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int M, int K, int N,
-                           int num_sms, cudaStream_t stream) {
+                           const ConvGeom &conv, int num_sms, cudaStream_t stream) {
     using Cfg = SlabCfg<BITS>;
     auto kern = slab_kernel<BITS, kFwd, ACC>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_FWD) != cudaSuccess)
         return LUTGEMM_E_CUDA;
     SlabArgs p{};
     p.a = a; p.w = w; p.lut = lut; p.gc = nullptr; p.out = c; p.M = M; p.K = K; p.N = N;
+    p.conv = conv;
     p.tiles_r = (M + Cfg::RT - 1) / Cfg::RT;
     p.tiles_c = (N + Cfg::CT - 1) / Cfg::CT;
     const long tiles = (long)p.tiles_r * p.tiles_c;
@@ -481,14 +499,14 @@ static int launch_fwd_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, cons
 }
 
 int forward_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K, int N,
-                 int num_sms, cudaStream_t stream) {
+                 const ConvGeom &conv, int num_sms, cudaStream_t stream) {
     const int acc = env_int("LUTGEMM_SLAB_ACC", 1);  // 1 measured fastest on B200 (0: +6 %, 2: +45 % time)
 #define LUTGEMM_CASE(B)                                                                         \
     case B:                                                                                     \
-        if (acc == 0) return launch_fwd_slab<B, 0>(a, w, c, lut, M, K, N, num_sms, stream);     \
-        if (acc == 2) return launch_fwd_slab<B, 2>(a, w, c, lut, M, K, N, num_sms, stream);     \
-        if (acc == 3) return launch_fwd_slab<B, 3>(a, w, c, lut, M, K, N, num_sms, stream);     \
-        return launch_fwd_slab<B, 1>(a, w, c, lut, M, K, N, num_sms, stream);
+        if (acc == 0) return launch_fwd_slab<B, 0>(a, w, c, lut, M, K, N, conv, num_sms, stream);     \
+        if (acc == 2) return launch_fwd_slab<B, 2>(a, w, c, lut, M, K, N, conv, num_sms, stream);     \
+        if (acc == 3) return launch_fwd_slab<B, 3>(a, w, c, lut, M, K, N, conv, num_sms, stream);     \
+        return launch_fwd_slab<B, 1>(a, w, c, lut, M, K, N, conv, num_sms, stream);
     switch (bits) {
         LUTGEMM_CASE(4)
         LUTGEMM_CASE(6)
@@ -499,12 +517,14 @@ int forward_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t
     return LUTGEMM_E_BITS;
 }
 
-int slab_reduce_blocks(const float *part, float *out, int K, int C, int nblocks, bool transpose, int num_sms,
-                       cudaStream_t stream) {
+int slab_reduce_blocks(const float *part, float *out, int K, int C, int nblocks, bool transpose, int bkl_L,
+                       int num_sms, cudaStream_t stream) {
     const long tiles = (long)((K + 31) / 32) * ((C + 31) / 32);
     const int rgrid = (int)(tiles < 8L * num_sms ? tiles : 8L * num_sms);
-    if (transpose) slab_reduce_blocks_kernel<true><<<rgrid, 256, 0, stream>>>(part, out, K, C, nblocks, kGradFactor);
-    else slab_reduce_blocks_kernel<false><<<rgrid, 256, 0, stream>>>(part, out, K, C, nblocks, kGradFactor);
+    if (transpose && bkl_L == 0)
+        slab_reduce_blocks_kernel<true><<<rgrid, 256, 0, stream>>>(part, out, K, C, nblocks, kGradFactor, 0);
+    else
+        slab_reduce_blocks_kernel<false><<<rgrid, 256, 0, stream>>>(part, out, K, C, nblocks, kGradFactor, bkl_L);
     return cudaGetLastError() == cudaSuccess ? LUTGEMM_OK : LUTGEMM_E_CUDA;
 }
 
@@ -513,7 +533,8 @@ int slab_grad_row_blocks(int rdim) { return (rdim + 511) / 512; }
 
 template <int BITS, int MODE>
 static int launch_grad_slab(const float *gc, const uint8_t *a, const uint8_t *w, float *out, const int16_t *lut,
-                            int M, int K, int N, float *scratch, int num_sms, cudaStream_t stream) {
+                            int M, int K, int N, const ConvGeom &conv, float *scratch, int num_sms,
+                            cudaStream_t stream) {
     using Cfg = SlabCfg<BITS>;
     auto kern = env_int("LUTGEMM_SLAB_CVT", 1) == 0 ? slab_kernel<BITS, MODE, 0> : slab_kernel<BITS, MODE, 1>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BWD) != cudaSuccess)
@@ -521,6 +542,8 @@ static int launch_grad_slab(const float *gc, const uint8_t *a, const uint8_t *w,
     const int RDIM = MODE == kGa ? N : M, CDIM = MODE == kGa ? M : N;
     SlabArgs p{};
     p.a = a; p.w = w; p.lut = lut; p.gc = gc; p.M = M; p.K = K; p.N = N;
+    p.conv = conv;
+    p.ga_bkl = (MODE == kGa && conv.enabled) ? 1 : 0;
     p.tiles_r = (RDIM + Cfg::RT - 1) / Cfg::RT;
     p.tiles_c = (CDIM + Cfg::CT - 1) / Cfg::CT;
     p.direct = p.tiles_r == 1;
@@ -535,28 +558,30 @@ static int launch_grad_slab(const float *gc, const uint8_t *a, const uint8_t *w,
     const int grid = (int)(items < num_sms ? items : num_sms);
     kern<<<grid, Cfg::THREADS, Cfg::SMEM_BWD, stream>>>(p);
     if (cudaGetLastError() != cudaSuccess) return LUTGEMM_E_CUDA;
-    if (!p.direct) return slab_reduce_blocks(scratch, out, K, CDIM, p.tiles_r, MODE == kGa, num_sms, stream);
+    if (!p.direct)
+        return slab_reduce_blocks(scratch, out, K, CDIM, p.tiles_r, MODE == kGa, p.ga_bkl ? conv.Ho * conv.Wo : 0,
+                                  num_sms, stream);
     return LUTGEMM_OK;
 }
 
 int backward_gw_slab(const float *gc, const uint8_t *a, const uint8_t *w, float *gw, const int16_t *lut_gw, int bits,
-                     int M, int K, int N, float *scratch, int num_sms, cudaStream_t stream) {
+                     int M, int K, int N, const ConvGeom &conv, float *scratch, int num_sms, cudaStream_t stream) {
     switch (bits) {
-        case 4: return launch_grad_slab<4, kGw>(gc, a, w, gw, lut_gw, M, K, N, scratch, num_sms, stream);
-        case 6: return launch_grad_slab<6, kGw>(gc, a, w, gw, lut_gw, M, K, N, scratch, num_sms, stream);
-        case 7: return launch_grad_slab<7, kGw>(gc, a, w, gw, lut_gw, M, K, N, scratch, num_sms, stream);
-        case 8: return launch_grad_slab<8, kGw>(gc, a, w, gw, lut_gw, M, K, N, scratch, num_sms, stream);
+        case 4: return launch_grad_slab<4, kGw>(gc, a, w, gw, lut_gw, M, K, N, conv, scratch, num_sms, stream);
+        case 6: return launch_grad_slab<6, kGw>(gc, a, w, gw, lut_gw, M, K, N, conv, scratch, num_sms, stream);
+        case 7: return launch_grad_slab<7, kGw>(gc, a, w, gw, lut_gw, M, K, N, conv, scratch, num_sms, stream);
+        case 8: return launch_grad_slab<8, kGw>(gc, a, w, gw, lut_gw, M, K, N, conv, scratch, num_sms, stream);
     }
     return LUTGEMM_E_BITS;
 }
 
 int backward_ga_slab(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, const int16_t *lut_ga, int bits,
-                     int M, int K, int N, float *scratch, int num_sms, cudaStream_t stream) {
+                     int M, int K, int N, const ConvGeom &conv, float *scratch, int num_sms, cudaStream_t stream) {
     switch (bits) {
-        case 4: return launch_grad_slab<4, kGa>(gc, a, w, ga, lut_ga, M, K, N, scratch, num_sms, stream);
-        case 6: return launch_grad_slab<6, kGa>(gc, a, w, ga, lut_ga, M, K, N, scratch, num_sms, stream);
-        case 7: return launch_grad_slab<7, kGa>(gc, a, w, ga, lut_ga, M, K, N, scratch, num_sms, stream);
-        case 8: return launch_grad_slab<8, kGa>(gc, a, w, ga, lut_ga, M, K, N, scratch, num_sms, stream);
+        case 4: return launch_grad_slab<4, kGa>(gc, a, w, ga, lut_ga, M, K, N, conv, scratch, num_sms, stream);
+        case 6: return launch_grad_slab<6, kGa>(gc, a, w, ga, lut_ga, M, K, N, conv, scratch, num_sms, stream);
+        case 7: return launch_grad_slab<7, kGa>(gc, a, w, ga, lut_ga, M, K, N, conv, scratch, num_sms, stream);
+        case 8: return launch_grad_slab<8, kGa>(gc, a, w, ga, lut_ga, M, K, N, conv, scratch, num_sms, stream);
     }
     return LUTGEMM_E_BITS;
 }

@@ -553,7 +553,7 @@ static int launch_grad_ws(const float *gc, const uint8_t *a, const uint8_t *w, f
     const int grid = (int)(items < num_sms ? items : num_sms);
     kern<<<grid, ws::kThreads, C::SMEM_BWD, stream>>>(p);
     if (cudaGetLastError() != cudaSuccess) return LUTGEMM_E_CUDA;
-    if (!p.direct) return slab_reduce_blocks(scratch, out, K, CDIM, p.tiles_r, MODE == ws::kGa, num_sms, stream);
+    if (!p.direct) return slab_reduce_blocks(scratch, out, K, CDIM, p.tiles_r, MODE == ws::kGa, 0, num_sms, stream);
     return LUTGEMM_OK;
 }
 

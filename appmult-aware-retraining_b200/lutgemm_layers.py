@@ -1,0 +1,166 @@
+"""Approximate-multiplier layers on top of the LUT-GEMM ops: `AppConv2d`, `AppLinear`, `prepare`.
+
+They follow the layer contract of the reference's `ApproxConv2d` (micronet+/app_layers.py:116-185):
+activation and weight are fake-quantised to unsigned b-bit codes with asymmetric (min/max) ranges -
+an exponential-moving-average observer for activations (momentum 0.1, :38-53) and a running min/max
+observer for weights (:21-35), scales and zero points refreshed every training step (:155-160) - the
+code x code product goes through the approximate multiplier, and the three zero-point cross terms of
+
+    (s_a (q_a + z_a)) * (s_w (q_w + z_w)) = s_a s_w (q_a q_w + z_w q_a + z_a q_w + z_a z_w)
+
+are exact (:175-181, equation 8 of the paper).  Rounding uses the straight-through estimator (:147-150).
+
+Differences from the reference, on purpose: the cross terms are computed as window sums (a one-channel
+box filter of the channel-summed codes, one batch-independent convolution of a ones image with the
+weight codes, a tap count) instead of three full convolutions - identical in exact arithmetic; linear
+layers go through the approximate multiplier too (`AppLinear`), which the reference's `QuantLinear`
+(:78-113) does not do; the convolution can use the fused implicit-im2col kernels instead of
+`F.unfold`.  Spatial padding is code 0 and therefore contributes LUT[0][w], as in the reference
+(self_ops/ops_py/approx_ops.py:556)."""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+import self_ops
+
+
+class _MinMax(nn.Module):
+    """Running min/max (weights) or exponential moving average of min/max (activations)."""
+
+    def __init__(self, momentum: float | None):
+        super().__init__()
+        self.momentum = momentum
+        self.register_buffer("min_val", torch.zeros(1))
+        self.register_buffer("max_val", torch.zeros(1))
+        self.register_buffer("seen", torch.zeros(1))
+
+    @torch.no_grad()
+    def update(self, x: torch.Tensor) -> None:
+        lo, hi = torch.aminmax(x)
+        first = self.seen == 0
+        if self.momentum is None:
+            new_lo, new_hi = torch.minimum(lo, self.min_val), torch.maximum(hi, self.max_val)
+        else:
+            new_lo = (1 - self.momentum) * self.min_val + self.momentum * lo
+            new_hi = (1 - self.momentum) * self.max_val + self.momentum * hi
+        self.min_val.copy_(torch.where(first, lo, new_lo))
+        self.max_val.copy_(torch.where(first, hi, new_hi))
+        self.seen.fill_(1)
+
+
+class _AppQuant(nn.Module):
+    """Shared quantisation state of the approximate layers."""
+
+    def _init_quant(self, a_bits: int, w_bits: int) -> None:
+        self.act_range = _MinMax(momentum=0.1)
+        self.weight_range = _MinMax(momentum=None)
+        self.a_qmax = float((1 << a_bits) - 1)
+        self.w_qmax = float((1 << w_bits) - 1)
+        for name in ("activation_scale", "weight_scale"):
+            self.register_buffer(name, torch.ones(1))
+        for name in ("activation_zp_neg", "weight_zp_neg"):
+            self.register_buffer(name, torch.zeros(1))
+
+    def _refresh(self, x: torch.Tensor, w: torch.Tensor) -> None:
+        if not self.training:
+            return
+        eps = torch.finfo(torch.float32).eps
+        with torch.no_grad():
+            self.act_range.update(x)
+            self.weight_range.update(w)
+            self.activation_scale.copy_(torch.clamp((self.act_range.max_val - self.act_range.min_val) / self.a_qmax, min=eps))
+            self.activation_zp_neg.copy_(torch.round(self.act_range.min_val / self.activation_scale))
+            self.weight_scale.copy_(torch.clamp((self.weight_range.max_val - self.weight_range.min_val) / self.w_qmax, min=eps))
+            self.weight_zp_neg.copy_(torch.round(self.weight_range.min_val / self.weight_scale))
+
+    @staticmethod
+    def _codes(x: torch.Tensor, scale: torch.Tensor, zp_neg: torch.Tensor, qmax: float) -> torch.Tensor:
+        """Float tensor of integer codes in [0, qmax]; gradient of the rounding is the identity."""
+        q = x / scale - zp_neg
+        q = q + (torch.round(q) - q).detach()
+        return torch.clamp(q, 0.0, qmax)
+
+
+class AppConv2d(nn.Conv2d, _AppQuant):
+    def __init__(self, in_channels, out_channels, kernel_size, stride=1, padding=0, dilation=1, groups=1, bias=True,
+                 a_bits=7, w_bits=7, use_ste_gradient=False, conv_impl="unfold"):
+        nn.Conv2d.__init__(self, in_channels, out_channels, kernel_size, stride, padding, dilation, groups, bias)
+        assert groups == 1, "groups is not supported in approximate convolution"
+        self._init_quant(a_bits, w_bits)
+        self.use_ste_gradient = use_ste_gradient
+        self.conv_impl = conv_impl
+
+    def _approx_conv(self, xq, wq):
+        kw = dict(bias=None, stride=self.stride, padding=self.padding, dilation=self.dilation, groups=1)
+        if self.use_ste_gradient:
+            return self_ops.approx_conv2d_baseline_op(xq, wq, **kw)
+        if self.conv_impl == "fused":
+            return self_ops.approx_conv2d_fused_op(xq, wq, **kw)
+        return self_ops.approx_conv2d_op(xq, wq, **kw)
+
+    def forward(self, x):
+        self._refresh(x, self.weight)
+        xq = self._codes(x, self.activation_scale, self.activation_zp_neg, self.a_qmax)
+        wq = self._codes(self.weight, self.weight_scale, self.weight_zp_neg, self.w_qmax)
+        geo = dict(stride=self.stride, padding=self.padding, dilation=self.dilation)
+        kh, kw_ = self.kernel_size
+        ones_k = torch.ones(1, 1, kh, kw_, device=x.device, dtype=x.dtype)
+        ones_img = torch.ones(1, 1, x.shape[2], x.shape[3], device=x.device, dtype=x.dtype)
+        # z_w * sum_{valid taps, channels} q_a ; z_a * sum_{valid taps} q_w ; z_a z_w * (#valid taps * Cin)
+        box_a = F.conv2d(xq.sum(dim=1, keepdim=True), ones_k, **geo)
+        sum_w = F.conv2d(ones_img.expand(1, self.in_channels, -1, -1), wq, **geo)
+        taps = F.conv2d(ones_img, ones_k, **geo) * float(self.in_channels)
+        acc = self._approx_conv(xq, wq) + self.weight_zp_neg * box_a + self.activation_zp_neg * sum_w \
+            + (self.activation_zp_neg * self.weight_zp_neg) * taps
+        out = (self.activation_scale * self.weight_scale) * acc
+        if self.bias is not None:
+            out = out + self.bias.view(1, -1, 1, 1)
+        return out
+
+
+class AppLinear(nn.Linear, _AppQuant):
+    def __init__(self, in_features, out_features, bias=True, a_bits=7, w_bits=7, use_ste_gradient=False):
+        nn.Linear.__init__(self, in_features, out_features, bias)
+        self._init_quant(a_bits, w_bits)
+        self.use_ste_gradient = use_ste_gradient
+
+    def forward(self, x):
+        self._refresh(x, self.weight)
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, self.in_features)
+        xq = self._codes(x2, self.activation_scale, self.activation_zp_neg, self.a_qmax)
+        wq = self._codes(self.weight, self.weight_scale, self.weight_zp_neg, self.w_qmax)
+        gemm = self_ops.approx_gemm_baseline_op if self.use_ste_gradient else self_ops.approx_gemm_op
+        acc = gemm(xq, wq.t()) + self.weight_zp_neg * xq.sum(dim=1, keepdim=True) \
+            + self.activation_zp_neg * wq.sum(dim=1).unsqueeze(0) \
+            + (self.activation_zp_neg * self.weight_zp_neg) * float(self.in_features)
+        out = (self.activation_scale * self.weight_scale) * acc
+        if self.bias is not None:
+            out = out + self.bias
+        return out.reshape(*lead, self.out_features)
+
+
+def prepare(model: nn.Module, a_bits: int = 7, w_bits: int = 7, use_ste_gradient: bool = False,
+            conv_impl: str = "unfold", linear: bool = True) -> nn.Module:
+    """Swaps every nn.Conv2d (and, with linear=True, nn.Linear) of `model` in place for its approximate
+    counterpart; parameters are shared with the replaced module (cf. add_quant_op,
+    micronet+/app_layers.py:270-339)."""
+    for name, child in list(model.named_children()):
+        if isinstance(child, (AppConv2d, AppLinear)):
+            continue
+        if isinstance(child, nn.Conv2d) and child.groups == 1:
+            new = AppConv2d(child.in_channels, child.out_channels, child.kernel_size, child.stride, child.padding,
+                            child.dilation, 1, child.bias is not None, a_bits, w_bits, use_ste_gradient, conv_impl)
+            new.weight = child.weight
+            new.bias = child.bias
+            setattr(model, name, new.to(child.weight.device))
+        elif linear and isinstance(child, nn.Linear):
+            new = AppLinear(child.in_features, child.out_features, child.bias is not None, a_bits, w_bits, use_ste_gradient)
+            new.weight = child.weight
+            new.bias = child.bias
+            setattr(model, name, new.to(child.weight.device))
+        else:
+            prepare(child, a_bits, w_bits, use_ste_gradient, conv_impl, linear)
+    return model

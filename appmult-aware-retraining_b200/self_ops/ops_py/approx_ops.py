@@ -162,3 +162,44 @@ def approx_conv2d_op(input, weight, bias, stride, padding, dilation, groups):
 def approx_conv2d_baseline_op(input, weight, bias, stride, padding, dilation, groups):
     """Same forward with the straight-through backward (reference approx_conv2d_baseline_op, :576-619)."""
     return _conv2d_via_gemm(approx_gemm_baseline_op, input, weight, bias, stride, padding, dilation, groups)
+
+
+class ApproxConv2dFused(Function):
+    """Approximate convolution with the im2col fused into the kernels' operand loaders: neither the
+    unfolded activations nor their uint8 copy ever reach HBM in the forward pass (the reference
+    materialises both, :556-563).  Same values and gradients as `approx_conv2d_op`."""
+
+    @staticmethod
+    def forward(ctx, input, weight, stride, padding, dilation):
+        B, Cin, H, W = input.shape
+        Cout, _, kh, kw = weight.shape
+        x_u8 = input.to(torch.uint8).contiguous()
+        wmat = weight.reshape(Cout, -1).t().to(torch.uint8).contiguous()  # [K, Cout], K ordered (cin, kh, kw)
+        Ho = (H + 2 * padding - dilation * (kh - 1) - 1) // stride + 1
+        Wo = (W + 2 * padding - dilation * (kw - 1) - 1) // stride + 1
+        if lut_appmult is None:
+            raise RuntimeError("lookup tables are not initialised: call init_lookup_tables first")
+        y = torch.empty((B * Ho * Wo, Cout), dtype=torch.uint32, device=input.device)
+        approx_ops.approx_conv2d_forward(x_u8, wmat, y, lut_appmult, kh, kw, stride, padding, dilation)
+        ctx.save_for_backward(x_u8, wmat)
+        ctx.geom = (kh, kw, stride, padding, dilation, tuple(weight.shape), Ho, Wo)
+        # rows are (b, oh, ow): an NCHW tensor in channels-last memory, no copy
+        return y.to(torch.float32).view(B, Ho, Wo, Cout).permute(0, 3, 1, 2)
+
+    @staticmethod
+    def backward(ctx, g_out):
+        x_u8, wmat = ctx.saved_tensors
+        kh, kw, stride, padding, dilation, wshape, Ho, Wo = ctx.geom
+        B, Cout = x_u8.shape[0], wshape[0]
+        gy = g_out.permute(0, 2, 3, 1).reshape(B * Ho * Wo, Cout).contiguous()
+        gx = torch.empty(x_u8.shape, dtype=torch.float32, device=gy.device)
+        gw = torch.empty(wmat.shape, dtype=torch.float32, device=gy.device)
+        approx_ops.approx_conv2d_backward(gy, x_u8, wmat, gx, gw, lut_grad_a, lut_grad_b, kh, kw, stride, padding, dilation)
+        return gx, gw.t().reshape(wshape), None, None, None
+
+
+def approx_conv2d_fused_op(input, weight, bias, stride, padding, dilation, groups):
+    """Drop-in for `approx_conv2d_op` (same arguments and results) running on the fused kernels."""
+    assert bias is None, "bias is not supported in approximate convolution"
+    assert groups == 1, "groups is not supported in approximate convolution"
+    return ApproxConv2dFused.apply(input, weight, stride[0], padding[0], dilation[0])

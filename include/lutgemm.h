@@ -80,6 +80,38 @@ int lutgemm_backward(const float *gc, const uint8_t *a, const uint8_t *w, float 
                      void *scratch, size_t scratch_bytes, void *stream);
 
 /*
+ * Convolution forward with the im2col fused into the operand loader (no unfolded tensor in HBM):
+ *   y[(b*Ho+oh)*Wo+ow, n] = sum_{c,i,j} lut[ x[b,c,oh*stride-pad+i*dil,ow*stride-pad+j*dil] * (2^bits+2) + wmat[(c*kh+i)*kw+j, n] ]
+ * with code 0 outside the image (spatial padding looks up lut[0][w], as in the reference).
+ *   x    [B,C,H,W] uint8 codes (NCHW)       wmat [C*kh*kw, Cout] uint8 (the weight viewed [Cout,-1], transposed)
+ *   y    [B*Ho*Wo, Cout] uint32, i.e. NHWC;  Ho = (H + 2*pad - dil*(kh-1) - 1)/stride + 1, Wo likewise
+ * Replaces approx_conv2d_op's F.pad + F.unfold + transpose/reshape + approx_gemm_forward chain,
+ * self_ops/ops_py/approx_ops.py:556-571 (square stride/padding/dilation, groups = 1, no bias, :545-547).
+ */
+int lutgemm_conv2d_forward(const uint8_t *x, const uint8_t *wmat, uint32_t *y, const uint16_t *lut, int bits,
+                           int B, int C, int H, int W, int Cout, int kh, int kw, int stride, int pad, int dil,
+                           void *stream);
+
+/* Scratch bytes lutgemm_conv2d_backward needs: the unfolded activation gradient [B][C*kh*kw][Ho*Wo] in
+ * fp32 plus what the gradient kernels need.  No counterpart in the reference. */
+size_t lutgemm_conv2d_backward_scratch_bytes(int bits, int B, int C, int H, int W, int Cout, int kh, int kw,
+                                             int stride, int pad, int dil);
+
+/*
+ * Convolution backward through the gradient tables, activations gathered on the fly as in the forward:
+ *   gw[(c*kh+i)*kw+j, n] = 1/16 * sum_m lut_gw[a[m,k]][wmat[k,n]] * gy[m,n]          ([C*kh*kw, Cout] fp32)
+ *   gx[b,c,h,w]          = col2im( 1/16 * sum_n gy[m,n] * lut_ga[a[m,k]][wmat[k,n]] )   ([B,C,H,W] fp32)
+ *   gy [B*Ho*Wo, Cout] fp32 (NHWC).  gx or gw may be NULL.  The unfolded activation gradient lives in
+ *   `scratch` ([B][K][Ho*Wo]) and is folded by a deterministic gather kernel.
+ * Replaces the autograd chain of approx_conv2d_op (unfold backward + approx_gemm_backward),
+ * self_ops/ops_py/approx_ops.py:181-205,556-571.
+ */
+int lutgemm_conv2d_backward(const float *gy, const uint8_t *x, const uint8_t *wmat, float *gx, float *gw,
+                            const int16_t *lut_ga, const int16_t *lut_gw, int bits, int B, int C, int H, int W,
+                            int Cout, int kh, int kw, int stride, int pad, int dil, void *scratch,
+                            size_t scratch_bytes, void *stream);
+
+/*
  * Weight gradient only, with no device memory taken from anyone: same result as lutgemm_backward with
  * ga == NULL, but the kernels' partial sums go to a fixed array inside the library image instead of a
  * caller-supplied scratch buffer.  Meant for callers that may not allocate when the gradient is due -

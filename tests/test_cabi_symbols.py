@@ -33,7 +33,8 @@ def test_header_declares_the_expected_entry_points():
     syms = declared_symbols()
     for s in ("lutgemm_forward", "lutgemm_backward", "lutgemm_backward_scratch_bytes", "lutgemm_lut_elem_num",
               "lutgemm_bits_from_elem_num", "lutgemm_status_string", "lutgemm_version", "lutgemm_device_error",
-              "lutgemm_selftest_bounded_wait"):
+              "lutgemm_selftest_bounded_wait", "lutgemm_conv2d_forward", "lutgemm_conv2d_backward",
+              "lutgemm_conv2d_backward_scratch_bytes", "lutgemm_backward_gw_noalloc"):
         assert s in syms
 
 

@@ -210,6 +210,62 @@ def test_autograd_ops_and_conv_against_golden(dev, golden):
     assert torch.allclose(a.grad, gc @ b.detach().t(), rtol=1e-4, atol=1e-2)
 
 
+CONV_CASES = [  # B, Cin, H, W, Cout, k, stride, pad, dil
+    (2, 3, 8, 8, 5, 3, 1, 1, 1), (1, 4, 9, 7, 6, 3, 2, 1, 1), (2, 2, 6, 6, 3, 1, 1, 0, 1), (1, 3, 10, 10, 4, 3, 1, 2, 2),
+    (3, 3, 32, 32, 64, 3, 1, 1, 1), (2, 16, 16, 16, 40, 3, 2, 1, 1), (4, 8, 12, 12, 32, 1, 2, 0, 1),
+    (2, 64, 16, 16, 64, 3, 1, 1, 1), (1, 24, 20, 20, 400, 3, 1, 1, 1), (2, 5, 7, 9, 33, 5, 1, 2, 1)]
+
+
+@pytest.mark.parametrize("bits", [4, 6, 7, 8])
+def test_fused_conv_kernels_against_oracle(dev, oracle_c, bits):
+    """lutgemm_conv2d_forward / _backward (implicit im2col) against im2col + GEMM + col2im on the oracle."""
+    import approx_ops
+    lf, la, lw = synth_wire(bits, seed=30 + bits)
+    lft, lat, lwt = (torch.from_numpy(t).to(dev) for t in (lf, la, lw))
+    for s_, (B, Cin, H, W, Cout, k, st, p, d) in enumerate(CONV_CASES):
+        rng = np.random.default_rng(1000 * bits + s_)
+        q = 1 << bits
+        x = rng.integers(0, q, (B, Cin, H, W)).astype(np.uint8)
+        wt = rng.integers(0, q, (Cout, Cin, k, k)).astype(np.uint8)
+        wmat = np.ascontiguousarray(wt.reshape(Cout, -1).T)
+        Ho, Wo = (H + 2 * p - d * (k - 1) - 1) // st + 1, (W + 2 * p - d * (k - 1) - 1) // st + 1
+        gy = rng.standard_normal((B * Ho * Wo, Cout)).astype(np.float32)
+        col = oracle_c.im2col(x, k, k, st, p, d)
+        want_y = oracle_c.forward(col, wmat, lf, bits)
+        xt, wm = torch.from_numpy(x).to(dev), torch.from_numpy(wmat).to(dev)
+        y = torch.full((B * Ho * Wo, Cout), 0xDEADBEEF, dtype=torch.uint32, device=dev)
+        approx_ops.approx_conv2d_forward(xt, wm, y, lft, k, k, st, p, d)
+        assert np.array_equal(y.cpu().numpy(), want_y), (bits, B, Cin, H, W, Cout, k, st, p, d)
+        gx = torch.full(x.shape, float("nan"), dtype=torch.float32, device=dev)
+        gw = torch.full(wmat.shape, float("nan"), dtype=torch.float32, device=dev)
+        approx_ops.approx_conv2d_backward(torch.from_numpy(gy).to(dev), xt, wm, gx, gw, lat, lwt, k, k, st, p, d)
+        r_ga, r_gw, r_gaa, r_gwa = oracle_c.backward_f64(gy, col, wmat, la, lw, bits)
+        gw_n, gx_n = gw.cpu().numpy(), gx.cpu().numpy()
+        assert (np.abs(gw_n - r_gw) <= TOL * r_gwa + 1e-30).all()
+        r_gx = O.col2im_f64(r_ga, x.shape, k, k, st, p, d)
+        r_gxa = O.col2im_f64(r_gaa, x.shape, k, k, st, p, d)
+        assert np.isfinite(gx_n).all()
+        assert (np.abs(gx_n - r_gx) <= TOL * r_gxa + 1e-30).all(), (bits, B, Cin, H, W, Cout, k, st, p, d)
+
+
+def test_fused_conv_op_against_golden(dev, golden):
+    """self_ops.approx_conv2d_fused_op must reproduce the golden conv fixtures like approx_conv2d_op does."""
+    import self_ops
+    bits = int(golden["bits"])
+    fp, ga_t, gb_t = (O.unpack_padded(golden[k], bits) for k in ("lut_fp", "lut_ga", "lut_gb"))
+    self_ops.set_lookup_tables(dev, fp, ga_t, gb_t, bits)
+    for i in range(4):
+        B, Cin, H, W, Cout, k, s, p, d = [int(v) for v in golden[f"conv{i}_cfg"]]
+        x = torch.from_numpy(golden[f"conv{i}_x"]).to(dev).float().requires_grad_(True)
+        wt = torch.from_numpy(golden[f"conv{i}_w"]).to(dev).float().requires_grad_(True)
+        y = self_ops.approx_conv2d_fused_op(x, wt, bias=None, stride=(s, s), padding=(p, p), dilation=(d, d), groups=1)
+        assert np.array_equal(y.detach().cpu().numpy(), golden[f"conv{i}_y"])
+        y.backward(torch.from_numpy(golden[f"conv{i}_gy"]).to(dev))
+        for got, want in ((x.grad, golden[f"conv{i}_gx"]), (wt.grad, golden[f"conv{i}_gw"])):
+            got = got.cpu().numpy()
+            assert np.abs(got - want).max() <= TOL * max(np.abs(want).max(), 1e-30)
+
+
 def test_errors_raise_instead_of_printing(dev):
     import approx_ops
     a = torch.zeros(4, 4, dtype=torch.uint8, device=dev)
