@@ -368,6 +368,124 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------------------
+# ResNet-18 (CIFAR shape) data-parallel training step
+# ------------------------------------------------------------------------------------------------
+def run_resnet18(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    import approx_ops
+    import self_ops
+    from lutgemm_dp import allreduce_grads_bucketed
+    from lutgemm_layers import prepare
+    from lutgemm_models import lut_macs_per_image, resnet18_cifar
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device for --impl ours (there is no CPU fallback)")
+    approx_ops.library()
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    bits, batch = args.bits, args.batch
+    L, qa, qb = synthetic_wire_tables(bits, 0)
+    self_ops.set_lookup_tables(dev, L, qa, qb, bits)
+    torch.manual_seed(0)  # identical initial weights on every rank
+    model = resnet18_cifar(10).to(dev)
+    macs_img = lut_macs_per_image(model)
+    prepare(model, a_bits=bits, w_bits=bits, conv_impl=args.conv_impl)
+    model = model.to(memory_format=torch.channels_last)
+    model.train()
+    opt = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9)
+    params = [p for p in model.parameters() if p.requires_grad]
+    g = torch.Generator().manual_seed(100 + rank)
+    nsets = 4
+    imgs_h = [torch.randn(batch, 3, 32, 32, generator=g).pin_memory() for _ in range(nsets)]
+    lbls_h = [torch.randint(0, 10, (batch,), generator=g).pin_memory() for _ in range(nsets)]
+    imgs_d = [t.to(dev) for t in imgs_h]
+    lbls_d = [t.to(dev) for t in lbls_h]
+
+    def step(x, y):
+        opt.zero_grad(set_to_none=True)
+        loss = F.cross_entropy(model(x), y)
+        loss.backward()
+        allreduce_grads_bucketed(params)
+        opt.step()
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(imgs_d[i % nsets], lbls_d[i % nsets])
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        step(imgs_d[i % nsets], lbls_d[i % nsets])
+    e1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = e0.elapsed_time(e1)
+    # end to end: images and labels from pinned host memory, loss read back, every step
+    e2e_steps = max(1, min(args.steps, 5))
+    barrier()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    for i in range(e2e_steps):
+        loss = step(imgs_h[i % nsets].to(dev, non_blocking=True), lbls_h[i % nsets].to(dev, non_blocking=True))
+        loss_value = float(loss.item())
+    e3.record()
+    barrier()
+    e2e_ms = e2.elapsed_time(e3)
+    if world > 1:
+        t = torch.tensor([total_ms, e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, e2e_ms = float(t[0]), float(t[1])
+    err = approx_ops.device_error()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peaks, peaks_kind = measured_peaks()
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    clk_max = float(peaks.get("sm_max_mhz") or 1965.0)
+    peak_lookups = sms * clk_max * 1e6 * LSU_LOOKUPS_PER_CLK_PER_SM
+    value = world * batch * args.steps / (total_ms * 1e-3)
+    macs_step = 3.0 * macs_img * batch
+    line = {
+        "metric": "appmult_resnet18_train_throughput", "value": value, "unit": "img/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u16 table -> u32 (fwd) / f32 (bwd) accumulate, f32 elsewhere",
+        "data": "synthetic",
+        "config": {"workload": f"ResNet-18 CIFAR-shape AppMult training step, {bits}-bit, batch {batch}/GPU, SGD",
+                   "bits": bits, "batch_per_gpu": batch, "conv_impl": args.conv_impl,
+                   "lut_macs_per_step_per_gpu": macs_step,
+                   "parallelism": f"dp{world} (batch sharded, bucketed NCCL all-reduce of gradients)" if world > 1 else "single GPU",
+                   "l2": f"{nsets} rotating batches; activations of a step exceed L2"},
+        "roofline": {"bound": "smem_lsu", "kernel": "whole step (LUT kernels + fp32 glue)",
+                     "achieved": macs_step * args.steps / (total_ms * 1e-3) / 1e9, "peak": peak_lookups / 1e9,
+                     "unit": "G lookups/s", "frac": macs_step * args.steps / (total_ms * 1e-3) / peak_lookups,
+                     "peak_def": f"{sms} SMs x {clk_max:.0f} MHz ({peaks_kind} sm_max_mhz) x 32 lookups/clk/SM", "traffic": None},
+        "cpu_baseline": None,
+        "e2e": {"value": world * batch * e2e_steps / (e2e_ms * 1e-3), "unit": "img/s",
+                "h2d_bytes_per_step": batch * (3 * 32 * 32 * 4 + 8), "d2h_bytes_per_step": 4, "steps": e2e_steps,
+                "ms_per_step": e2e_ms / e2e_steps, "last_loss": loss_value},
+        "gpu_launches": None, "clocks": clocks, "device_error": err,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -377,6 +495,9 @@ def main():
     ap.add_argument("--bits", type=int, default=8, choices=[4, 6, 7, 8])
     ap.add_argument("--size", type=int, default=4096)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", choices=["lutgemm", "resnet18"], default="lutgemm")
+    ap.add_argument("--batch", type=int, default=256, help="per-GPU batch of the resnet18 workload")
+    ap.add_argument("--conv-impl", choices=["fused", "unfold"], default="fused")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -384,6 +505,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference_arm(args, rank, world)
+    elif args.workload == "resnet18":
+        if "--bits" not in sys.argv:
+            args.bits = 7
+        run_resnet18(args, rank, world, local_rank)
     else:
         run_ours(args, rank, world, local_rank)
 
