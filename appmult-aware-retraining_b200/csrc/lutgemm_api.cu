@@ -48,21 +48,25 @@ struct BackwardPlan {
 // LUTGEMM_BACKWARD_KERNEL=bcast|slab overrides (for A/B timing).
 BackwardPlan plan_backward(int bits, int M, int K, int N, int sms) {
     BackwardPlan pl{};
-    // measured on B200 at 4096^3: the gradient slab kernels beat the broadcast kernels only where the
-    // latter suffer bank conflicts (7 and 8 bits); at 4 and 6 bits a table row is conflict-free already
+    // measured on B200 at 4096^3 (ms, grad_w / grad_a): fp32-slab 19.8 / 20.7 (8 bit), 16.9 / 16.9 (7 bit),
+    // 15.3 / 15.3 (6 bit) against broadcast 24.5 / 23.9, 18.4 / 17.9, 12.0 / 13.0: the slab kernels win
+    // where the broadcast gathers suffer bank conflicts (7 and 8 bits); at 4 and 6 bits a table row is
+    // conflict-free already
     pl.gw_slab = bits >= 7 && M >= 512 && N >= 32 && slab_fill(M, N) >= 0.6;
     pl.ga_slab = bits >= 7 && N >= 384 && M >= 32 && slab_fill(N, M) >= 0.6;
     if (env_is("LUTGEMM_BACKWARD_KERNEL", "bcast")) pl.gw_slab = pl.ga_slab = false;
     if (env_is("LUTGEMM_BACKWARD_KERNEL", "slab")) pl.gw_slab = pl.ga_slab = true;
+    // the fp32-slab kernels cut the reduction dimension into 384-row blocks, the others into 512-row
+    // blocks; scratch is sized for the smaller block (more partial sums) so every variant fits
     pl.gw_splits = pl.gw_slab ? 1 : lutgemm::gw_num_splits(bits, M, K, N, sms);
     if (pl.gw_slab) {
-        const int rb = lutgemm::slab_grad_row_blocks(M);
+        const int rb = lutgemm::slab_f32_row_blocks(M);
         pl.gw_scratch = rb > 1 ? (size_t)rb * K * N * sizeof(float) : 0;
     } else {
         pl.gw_scratch = pl.gw_splits > 1 ? (size_t)pl.gw_splits * K * N * sizeof(float) : 0;
     }
     if (pl.ga_slab) {
-        const int rb = lutgemm::slab_grad_row_blocks(N);
+        const int rb = lutgemm::slab_f32_row_blocks(N);
         pl.ga_scratch = rb > 1 ? (size_t)rb * K * M * sizeof(float) : 0;
     }
     return pl;
@@ -166,19 +170,22 @@ static int backward_impl(const float *gc, const uint8_t *a, const uint8_t *w, fl
     const BackwardPlan pl = plan_backward(bits, M, K, N, sms);
     float *sc = static_cast<float *>(scratch);
     const bool ws_impl = !conv.enabled && env_is("LUTGEMM_SLAB_IMPL", "ws");
+    const bool i16_impl = env_is("LUTGEMM_SLAB_IMPL", "sync");  // the int16-slab gradient kernels (A/B timing)
     if (gw) {
         // the weight gradient goes first: under data parallelism its all-reduce can then overlap gA
         if (pl.gw_scratch && (!scratch || scratch_bytes < pl.gw_scratch)) return LUTGEMM_E_SCRATCH;
         int rc = !pl.gw_slab ? lutgemm::backward_gw(gc, a, w, gw, lut_gw, bits, M, K, N, conv, sc, pl.gw_splits, sms, s)
                  : ws_impl   ? lutgemm::backward_gw_slab_ws(gc, a, w, gw, lut_gw, bits, M, K, N, sc, sms, s)
-                             : lutgemm::backward_gw_slab(gc, a, w, gw, lut_gw, bits, M, K, N, conv, sc, sms, s);
+                 : i16_impl  ? lutgemm::backward_gw_slab(gc, a, w, gw, lut_gw, bits, M, K, N, conv, sc, sms, s)
+                             : lutgemm::backward_gw_slab_f32(gc, a, w, gw, lut_gw, bits, M, K, N, conv, sc, sms, s);
         if (rc != LUTGEMM_OK) return rc;
     }
     if (ga) {
         if (pl.ga_scratch && (!scratch || scratch_bytes < pl.ga_scratch)) return LUTGEMM_E_SCRATCH;
         int rc = !pl.ga_slab ? lutgemm::backward_ga(gc, a, w, ga, lut_ga, bits, M, K, N, conv, sms, s)
                  : ws_impl   ? lutgemm::backward_ga_slab_ws(gc, a, w, ga, lut_ga, bits, M, K, N, sc, sms, s)
-                             : lutgemm::backward_ga_slab(gc, a, w, ga, lut_ga, bits, M, K, N, conv, sc, sms, s);
+                 : i16_impl  ? lutgemm::backward_ga_slab(gc, a, w, ga, lut_ga, bits, M, K, N, conv, sc, sms, s)
+                             : lutgemm::backward_ga_slab_f32(gc, a, w, ga, lut_ga, bits, M, K, N, conv, sc, sms, s);
         if (rc != LUTGEMM_OK) return rc;
     }
     return LUTGEMM_OK;

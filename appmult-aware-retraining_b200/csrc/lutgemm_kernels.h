@@ -19,6 +19,16 @@ int backward_gw_slab(const float *gc, const uint8_t *a, const uint8_t *w, float 
                      int M, int K, int N, const ConvGeom &conv, float *scratch, int num_sms, cudaStream_t stream);
 int backward_ga_slab(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, const int16_t *lut_ga, int bits,
                      int M, int K, int N, const ConvGeom &conv, float *scratch, int num_sms, cudaStream_t stream);
+// rows of the reduction dimension per CTA tile of the fp32-slab gradient kernels, and the block count
+constexpr int kSlabF32Rows = 512;
+int slab_f32_row_blocks(int rdim);
+// gradient slab kernels with an fp32 slab (conversion done once per slab entry, in the build)
+int backward_gw_slab_f32(const float *gc, const uint8_t *a, const uint8_t *w, float *gw, const int16_t *lut_gw,
+                         int bits, int M, int K, int N, const ConvGeom &conv, float *scratch, int num_sms,
+                         cudaStream_t stream);
+int backward_ga_slab_f32(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, const int16_t *lut_ga,
+                         int bits, int M, int K, int N, const ConvGeom &conv, float *scratch, int num_sms,
+                         cudaStream_t stream);
 // warp-specialised variants of the three slab kernels (producer warps build slabs, consumer warps gather)
 int forward_slab_ws(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K,
                     int N, int num_sms, cudaStream_t stream);

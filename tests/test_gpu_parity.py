@@ -109,12 +109,13 @@ def test_each_forward_kernel_on_every_shape_class(dev, oracle_c, bits, kernel, m
         assert np.array_equal(run_forward(dev, a, w, lf), oracle_c.forward(a, w, lf, bits)), (kernel, bits, M, K, N)
 
 
-@pytest.mark.parametrize("kernel", ["bcast", "slab", "slab-ws"])
+@pytest.mark.parametrize("kernel", ["bcast", "slab-f32", "slab-sync", "slab-ws"])
 @pytest.mark.parametrize("bits", [4, 6, 7, 8])
 def test_each_backward_kernel_on_every_shape_class(dev, oracle_c, bits, kernel, monkeypatch):
-    """Every family of gradient kernels (LUTGEMM_BACKWARD_KERNEL / LUTGEMM_SLAB_IMPL) on shapes of either class."""
+    """Every family of gradient kernels (LUTGEMM_BACKWARD_KERNEL / LUTGEMM_SLAB_IMPL: fp32 slab, int16 slab,
+    warp-specialised int16 slab, broadcast) on shapes of either class."""
     monkeypatch.setenv("LUTGEMM_BACKWARD_KERNEL", kernel.split("-")[0])
-    monkeypatch.setenv("LUTGEMM_SLAB_IMPL", "ws" if kernel.endswith("-ws") else "sync")
+    monkeypatch.setenv("LUTGEMM_SLAB_IMPL", kernel.split("-")[1] if "-" in kernel else "f32")
     _, la, lw = synth_wire(bits, seed=20 + bits)
     for s, (M, K, N) in enumerate([(1, 1, 1), (5, 33, 3), (130, 16, 64), (515, 31, 67), (1024, 48, 128), (66, 35, 520)]):
         a, w, gc = rand_problem(bits, M, K, N, seed=11 * bits + s)
