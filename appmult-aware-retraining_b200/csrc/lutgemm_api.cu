@@ -56,8 +56,6 @@ BackwardPlan plan_backward(int bits, int M, int K, int N, int sms) {
     pl.ga_slab = bits >= 7 && N >= 384 && M >= 32 && slab_fill(N, M) >= 0.6;
     if (env_is("LUTGEMM_BACKWARD_KERNEL", "bcast")) pl.gw_slab = pl.ga_slab = false;
     if (env_is("LUTGEMM_BACKWARD_KERNEL", "slab")) pl.gw_slab = pl.ga_slab = true;
-    // the fp32-slab kernels cut the reduction dimension into 384-row blocks, the others into 512-row
-    // blocks; scratch is sized for the smaller block (more partial sums) so every variant fits
     pl.gw_splits = pl.gw_slab ? 1 : lutgemm::gw_num_splits(bits, M, K, N, sms);
     if (pl.gw_slab) {
         const int rb = lutgemm::slab_f32_row_blocks(M);
@@ -170,13 +168,11 @@ static int backward_impl(const float *gc, const uint8_t *a, const uint8_t *w, fl
     const BackwardPlan pl = plan_backward(bits, M, K, N, sms);
     float *sc = static_cast<float *>(scratch);
     const bool ws_impl = !conv.enabled && env_is("LUTGEMM_SLAB_IMPL", "ws");
-    const bool i16_impl = env_is("LUTGEMM_SLAB_IMPL", "sync");  // the int16-slab gradient kernels (A/B timing)
     if (gw) {
         // the weight gradient goes first: under data parallelism its all-reduce can then overlap gA
         if (pl.gw_scratch && (!scratch || scratch_bytes < pl.gw_scratch)) return LUTGEMM_E_SCRATCH;
         int rc = !pl.gw_slab ? lutgemm::backward_gw(gc, a, w, gw, lut_gw, bits, M, K, N, conv, sc, pl.gw_splits, sms, s)
                  : ws_impl   ? lutgemm::backward_gw_slab_ws(gc, a, w, gw, lut_gw, bits, M, K, N, sc, sms, s)
-                 : i16_impl  ? lutgemm::backward_gw_slab(gc, a, w, gw, lut_gw, bits, M, K, N, conv, sc, sms, s)
                              : lutgemm::backward_gw_slab_f32(gc, a, w, gw, lut_gw, bits, M, K, N, conv, sc, sms, s);
         if (rc != LUTGEMM_OK) return rc;
     }
@@ -184,7 +180,6 @@ static int backward_impl(const float *gc, const uint8_t *a, const uint8_t *w, fl
         if (pl.ga_scratch && (!scratch || scratch_bytes < pl.ga_scratch)) return LUTGEMM_E_SCRATCH;
         int rc = !pl.ga_slab ? lutgemm::backward_ga(gc, a, w, ga, lut_ga, bits, M, K, N, conv, sms, s)
                  : ws_impl   ? lutgemm::backward_ga_slab_ws(gc, a, w, ga, lut_ga, bits, M, K, N, sc, sms, s)
-                 : i16_impl  ? lutgemm::backward_ga_slab(gc, a, w, ga, lut_ga, bits, M, K, N, conv, sc, sms, s)
                              : lutgemm::backward_ga_slab_f32(gc, a, w, ga, lut_ga, bits, M, K, N, conv, sc, sms, s);
         if (rc != LUTGEMM_OK) return rc;
     }

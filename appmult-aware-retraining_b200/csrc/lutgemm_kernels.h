@@ -15,10 +15,6 @@ int forward_rowbcast(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint
 int forward_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K, int N,
                  const ConvGeom &conv, int num_sms, cudaStream_t stream);
 
-int backward_gw_slab(const float *gc, const uint8_t *a, const uint8_t *w, float *gw, const int16_t *lut_gw, int bits,
-                     int M, int K, int N, const ConvGeom &conv, float *scratch, int num_sms, cudaStream_t stream);
-int backward_ga_slab(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, const int16_t *lut_ga, int bits,
-                     int M, int K, int N, const ConvGeom &conv, float *scratch, int num_sms, cudaStream_t stream);
 // rows of the reduction dimension per CTA tile of the fp32-slab gradient kernels, and the block count
 constexpr int kSlabF32Rows = 512;
 int slab_f32_row_blocks(int rdim);
@@ -44,8 +40,6 @@ int slab_ws_bounded_wait_selftest(cudaStream_t stream);
 int slab_reduce_blocks(const float *part, float *out, int K, int C, int nblocks, bool transpose, int bkl_L,
                        int num_sms, cudaStream_t stream);
 
-// number of 512-row blocks the slab gradient kernels cut their reduction dimension into
-int slab_grad_row_blocks(int rdim);
 
 // gx[B,C,H,W] from the unfolded activation gradient gcol[B][C*kh*kw][Ho*Wo] (deterministic gather)
 int col2im_gather(const float *gcol, float *gx, const ConvGeom &g, cudaStream_t stream);

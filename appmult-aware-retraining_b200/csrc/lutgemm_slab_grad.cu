@@ -337,6 +337,52 @@ __global__ void __launch_bounds__(32 * WARPS, 1) slab_grad_kernel(const Args p) 
 
 int slab_f32_row_blocks(int rdim) { return (rdim + kSlabF32Rows - 1) / kSlabF32Rows; }
 
+// out[k][c] (TRANSPOSE=false) or out[c][k] (TRANSPOSE=true) = scale * sum_b part[b][k][c], b ascending.
+// With bkl_L > 0 (and TRANSPOSE=false) column c = b*L + l goes to out[(b*K + k)*L + l] instead.
+template <bool TRANSPOSE>
+__global__ void slab_reduce_blocks_kernel(const float *__restrict__ part, float *__restrict__ out, int K, int C,
+                                          int nblocks, float scale, int bkl_L) {
+    __shared__ float tile[32][33];
+    const int tiles_c = (C + 31) / 32, tiles_k = (K + 31) / 32;
+    const size_t KC_ = (size_t)K * C;
+    for (int t = blockIdx.x; t < tiles_c * tiles_k; t += gridDim.x) {
+        const int k0 = (t / tiles_c) * 32, c0 = (t % tiles_c) * 32;
+        const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8 threads
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int k = k0 + ty + 8 * j, c = c0 + tx;
+            float s = 0.f;
+            if (k < K && c < C)
+                for (int b = 0; b < nblocks; ++b) s += part[(size_t)b * KC_ + (size_t)k * C + c];
+            if (TRANSPOSE) tile[ty + 8 * j][tx] = s * scale;
+            else if (k < K && c < C) {
+                if (bkl_L > 0) out[((size_t)(c / bkl_L) * K + k) * bkl_L + c % bkl_L] = s * scale;
+                else out[(size_t)k * C + c] = s * scale;
+            }
+        }
+        if (TRANSPOSE) {
+            __syncthreads();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int c = c0 + ty + 8 * j, k = k0 + tx;
+                if (k < K && c < C) out[(size_t)c * K + k] = tile[tx][ty + 8 * j];
+            }
+            __syncthreads();
+        }
+    }
+}
+
+int slab_reduce_blocks(const float *part, float *out, int K, int C, int nblocks, bool transpose, int bkl_L,
+                       int num_sms, cudaStream_t stream) {
+    const long tiles = (long)((K + 31) / 32) * ((C + 31) / 32);
+    const int rgrid = (int)(tiles < 8L * num_sms ? tiles : 8L * num_sms);
+    if (transpose && bkl_L == 0)
+        slab_reduce_blocks_kernel<true><<<rgrid, 256, 0, stream>>>(part, out, K, C, nblocks, kGradFactor, 0);
+    else
+        slab_reduce_blocks_kernel<false><<<rgrid, 256, 0, stream>>>(part, out, K, C, nblocks, kGradFactor, bkl_L);
+    return cudaGetLastError() == cudaSuccess ? LUTGEMM_OK : LUTGEMM_E_CUDA;
+}
+
 template <int BITS, int MODE, int WARPS, int RW, int PF>
 static int launch_slab_grad_w(const float *gc, const uint8_t *a, const uint8_t *w, float *out, const int16_t *lut,
                             int M, int K, int N, const ConvGeom &conv, float *scratch, int num_sms,
@@ -386,9 +432,6 @@ template <int BITS, int MODE>
 static int launch_slab_grad(const float *gc, const uint8_t *a, const uint8_t *w, float *out, const int16_t *lut,
                             int M, int K, int N, const ConvGeom &conv, float *scratch, int num_sms,
                             cudaStream_t stream) {
-    const char *e = getenv("LUTGEMM_SLAB_GRAD_VARIANT");
-    const int v = e ? atoi(e) : 0;
-    (void)v;
     return launch_slab_grad_w<BITS, MODE, 16, 32, 4>(gc, a, w, out, lut, M, K, N, conv, scratch, num_sms, stream);
 }
 

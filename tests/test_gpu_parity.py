@@ -109,10 +109,10 @@ def test_each_forward_kernel_on_every_shape_class(dev, oracle_c, bits, kernel, m
         assert np.array_equal(run_forward(dev, a, w, lf), oracle_c.forward(a, w, lf, bits)), (kernel, bits, M, K, N)
 
 
-@pytest.mark.parametrize("kernel", ["bcast", "slab-f32", "slab-sync", "slab-ws"])
+@pytest.mark.parametrize("kernel", ["bcast", "slab-f32", "slab-ws"])
 @pytest.mark.parametrize("bits", [4, 6, 7, 8])
 def test_each_backward_kernel_on_every_shape_class(dev, oracle_c, bits, kernel, monkeypatch):
-    """Every family of gradient kernels (LUTGEMM_BACKWARD_KERNEL / LUTGEMM_SLAB_IMPL: fp32 slab, int16 slab,
+    """Every family of gradient kernels (LUTGEMM_BACKWARD_KERNEL / LUTGEMM_SLAB_IMPL: fp32 slab,
     warp-specialised int16 slab, broadcast) on shapes of either class."""
     monkeypatch.setenv("LUTGEMM_BACKWARD_KERNEL", kernel.split("-")[0])
     monkeypatch.setenv("LUTGEMM_SLAB_IMPL", kernel.split("-")[1] if "-" in kernel else "f32")
