@@ -339,7 +339,11 @@ def run_ours(args, rank, world, local_rank):
         "per_kernel_ms": {n: float(t) for n, t in zip(names, kern_ms)},
         "hbm": {"achieved_gbs": alg_bytes[dom] / (kern_ms[dom] * 1e-3) / 1e9, "peak_gbs": peaks["hbm_gbs"],
                 "frac": alg_bytes[dom] / (kern_ms[dom] * 1e-3) / 1e9 / peaks["hbm_gbs"], "of": peaks_kind},
-        "traffic": None,
+        # dram__bytes_read.sum + dram__bytes_write.sum per launch of that kernel from the ncu capture
+        # summarised in profiles/slab_kernels_b8_4096.md (only that configuration was captured)
+        "traffic": ({"forward": 114.9e6, "grad_w": 638.7e6, "grad_a": 633.7e6}[names[dom]]
+                    if (bits, S) == (8, 4096) else None),
+        "traffic_unit": "bytes per launch (ncu, 8-bit 4096^3)",
     }
 
     cpu = None
