@@ -227,32 +227,37 @@ def approx_conv2d_backward(gy: torch.Tensor, x: torch.Tensor, wmat: torch.Tensor
                            lut_grad_a: torch.Tensor, lut_grad_b: torch.Tensor, kh: int, kw: int, stride: int, pad: int,
                            dil: int) -> None:
     """Fused-im2col convolution backward.  gy: f32 [B*Ho*Wo, Cout]; gx: f32 [B,C,H,W] and gw: f32
-    [C*kh*kw, Cout] are written in place."""
+    [C*kh*kw, Cout] are written in place; either may be None to skip that gradient."""
     _check_input(gy, torch.float32, "grad_output_tensor")
     _check_input(x, torch.uint8, "input_tensor")
     _check_input(wmat, torch.uint8, "weight_tensor")
-    _check_input(gx, torch.float32, "grad_input_tensor")
-    _check_input(gw, torch.float32, "grad_weight_tensor")
+    if gx is not None:
+        _check_input(gx, torch.float32, "grad_input_tensor")
+    if gw is not None:
+        _check_input(gw, torch.float32, "grad_weight_tensor")
     _check_input(lut_grad_a, torch.int16, "lut_grad_a_tensor")
     _check_input(lut_grad_b, torch.int16, "lut_grad_b_tensor")
     B, C, H, W = x.shape
     K, Cout = wmat.shape
     Ho, Wo = _conv_out(H, W, kh, kw, stride, pad, dil)
-    if K != C * kh * kw or tuple(gy.shape) != (B * Ho * Wo, Cout) or tuple(gx.shape) != tuple(x.shape) \
-            or tuple(gw.shape) != (K, Cout):
+    if K != C * kh * kw or tuple(gy.shape) != (B * Ho * Wo, Cout) \
+            or (gx is not None and tuple(gx.shape) != tuple(x.shape)) \
+            or (gw is not None and tuple(gw.shape) != (K, Cout)):
         raise RuntimeError("approx_conv2d_backward: tensor shapes do not match the convolution geometry")
     bits = _bits_of(lut_grad_a, "lut_grad_a_tensor")
     if _bits_of(lut_grad_b, "lut_grad_b_tensor") != bits:
         raise RuntimeError("lut_grad_a_tensor and lut_grad_b_tensor must have the same length")
     dev = gy.device
     for t in (x, wmat, gx, gw, lut_grad_a, lut_grad_b):
-        if t.device != dev:
+        if t is not None and t.device != dev:
             raise RuntimeError("All tensors should be on the same device")
     lib = _load()
     with torch.cuda.device(dev):
         nbytes = lib.lutgemm_conv2d_backward_scratch_bytes(bits, B, C, H, W, Cout, kh, kw, stride, pad, dil)
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
-        rc = lib.lutgemm_conv2d_backward(gy.data_ptr(), x.data_ptr(), wmat.data_ptr(), gx.data_ptr(), gw.data_ptr(),
+        rc = lib.lutgemm_conv2d_backward(gy.data_ptr(), x.data_ptr(), wmat.data_ptr(),
+                                         gx.data_ptr() if gx is not None else None,
+                                         gw.data_ptr() if gw is not None else None,
                                          lut_grad_a.data_ptr(), lut_grad_b.data_ptr(), bits, B, C, H, W, Cout, kh, kw,
                                          stride, pad, dil, scratch.data_ptr(), nbytes, _stream_ptr(dev))
     _check(rc, "approx_conv2d_backward")

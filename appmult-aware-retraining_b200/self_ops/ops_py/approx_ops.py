@@ -192,10 +192,13 @@ class ApproxConv2dFused(Function):
         kh, kw, stride, padding, dilation, wshape, Ho, Wo = ctx.geom
         B, Cout = x_u8.shape[0], wshape[0]
         gy = g_out.permute(0, 2, 3, 1).reshape(B * Ho * Wo, Cout).contiguous()
-        gx = torch.empty(x_u8.shape, dtype=torch.float32, device=gy.device)
-        gw = torch.empty(wmat.shape, dtype=torch.float32, device=gy.device)
-        approx_ops.approx_conv2d_backward(gy, x_u8, wmat, gx, gw, lut_grad_a, lut_grad_b, kh, kw, stride, padding, dilation)
-        return gx, gw.t().reshape(wshape), None, None, None
+        # a gradient nobody asked for (e.g. w.r.t. the input image of the first layer) is not computed
+        gx = torch.empty(x_u8.shape, dtype=torch.float32, device=gy.device) if ctx.needs_input_grad[0] else None
+        gw = torch.empty(wmat.shape, dtype=torch.float32, device=gy.device) if ctx.needs_input_grad[1] else None
+        if gx is not None or gw is not None:
+            approx_ops.approx_conv2d_backward(gy, x_u8, wmat, gx, gw, lut_grad_a, lut_grad_b, kh, kw, stride, padding,
+                                              dilation)
+        return gx, (gw.t().reshape(wshape) if gw is not None else None), None, None, None
 
 
 def approx_conv2d_fused_op(input, weight, bias, stride, padding, dilation, groups):

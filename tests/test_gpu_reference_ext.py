@@ -1,0 +1,57 @@
+"""GPU test against the reference's own CUDA operator (second oracle for the backward pass).
+
+oracle/build_reference_ext.py compiles the reference's unmodified kernel sources for sm_100a into
+oracle/_ref/ (one module per bit-width, built in the development container; the files travel to the GPU
+box, the sources do not).  Where a module is present, the library's results are compared with what the
+reference's kernels return for the same inputs: forward bit-exact, backward within 1e-5 of the largest
+gradient magnitude.  K is kept a multiple of 8 at 8 bits: there the reference pads its K tiles with a
+code that wraps to 0 and adds LUT[0][0] per padded k (a quirk this library does not reproduce)."""
+import glob
+import importlib.util
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle_np as O
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _load_ref(bits):
+    hits = glob.glob(os.path.join(ROOT, "oracle", "_ref", f"approx_ops_ref{bits}*.so"))
+    if not hits:
+        pytest.skip(f"oracle/_ref/approx_ops_ref{bits} has not been built")
+    spec = importlib.util.spec_from_file_location(f"approx_ops_ref{bits}", hits[0])
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+@pytest.mark.parametrize("bits", [7, 8])
+def test_against_the_reference_cuda_operator(bits):
+    assert torch.cuda.is_available(), "gpu-marked test started without a CUDA device"
+    ref = _load_ref(bits)
+    import approx_ops
+    dev = torch.device("cuda:0")
+    lf, la, lw = (torch.from_numpy(t).to(dev) for t in O.to_wire(*O.synthetic_tables(bits, seed=40 + bits), bits))
+    for s, (M, K, N) in enumerate([(64, 64, 64), (130, 72, 66), (512, 256, 320), (1024, 576, 64), (2048, 512, 512)]):
+        g = torch.Generator().manual_seed(50 * bits + s)
+        a = torch.randint(0, 1 << bits, (M, K), generator=g, dtype=torch.uint8).to(dev)
+        w = torch.randint(0, 1 << bits, (K, N), generator=g, dtype=torch.uint8).to(dev)
+        gc = torch.randn(M, N, generator=g).to(dev)
+        c_ref = torch.zeros(M, N, dtype=torch.uint32, device=dev)
+        ref.approx_gemm_forward(a, w, c_ref, lf)
+        c = torch.zeros(M, N, dtype=torch.uint32, device=dev)
+        approx_ops.approx_gemm_forward(a, w, c, lf)
+        torch.cuda.synchronize()
+        assert torch.equal(c.view(torch.int32), c_ref.view(torch.int32)), (bits, M, K, N)
+        ga_ref, gw_ref = torch.zeros(M, K, device=dev), torch.zeros(K, N, device=dev)
+        ref.approx_gemm_backward(gc, a, w, ga_ref, gw_ref, la, lw)
+        ga, gw = torch.zeros(M, K, device=dev), torch.zeros(K, N, device=dev)
+        approx_ops.approx_gemm_backward(gc, a, w, ga, gw, la, lw)
+        torch.cuda.synchronize()
+        for got, want in ((ga, ga_ref), (gw, gw_ref)):
+            assert float((got - want).abs().max()) <= 1e-5 * max(float(want.abs().max()), 1e-30), (bits, M, K, N)
