@@ -382,9 +382,8 @@ def run_resnet18(args, rank, world, local_rank):
 
     import approx_ops
     import self_ops
-    from lutgemm_dp import allreduce_grads_bucketed
-    from lutgemm_layers import prepare
     from lutgemm_models import lut_macs_per_image, resnet18_cifar
+    from lutgemm_train import build, train_step
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device for --impl ours (there is no CPU fallback)")
@@ -396,13 +395,8 @@ def run_resnet18(args, rank, world, local_rank):
     bits, batch = args.bits, args.batch
     L, qa, qb = synthetic_wire_tables(bits, 0)
     self_ops.set_lookup_tables(dev, L, qa, qb, bits)
-    torch.manual_seed(0)  # identical initial weights on every rank
-    model = resnet18_cifar(10).to(dev)
-    macs_img = lut_macs_per_image(model)
-    prepare(model, a_bits=bits, w_bits=bits, conv_impl=args.conv_impl)
-    model = model.to(memory_format=torch.channels_last)
-    model.train()
-    opt = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9)
+    macs_img = lut_macs_per_image(resnet18_cifar(10).to(dev))
+    model, opt = build(dev, bits, conv_impl=args.conv_impl)
     params = [p for p in model.parameters() if p.requires_grad]
     g = torch.Generator().manual_seed(100 + rank)
     nsets = 4
@@ -412,12 +406,7 @@ def run_resnet18(args, rank, world, local_rank):
     lbls_d = [t.to(dev) for t in lbls_h]
 
     def step(x, y):
-        opt.zero_grad(set_to_none=True)
-        loss = F.cross_entropy(model(x), y)
-        loss.backward()
-        allreduce_grads_bucketed(params)
-        opt.step()
-        return loss
+        return train_step(model, opt, params, x, y)
 
     def barrier():
         if world > 1:
