@@ -31,6 +31,12 @@ double slab_fill(long rows, long cols) {
     return (double)rows * (double)cols / ((double)tr * 512.0 * (double)tc * 64.0);
 }
 
+// tile fill of a [rows x cols] problem cut into 1024 x 32 slab tiles
+double tall_fill(long rows, long cols) {
+    const long tr = (rows + 1023) / 1024, tc = (cols + 31) / 32;
+    return (double)rows * (double)cols / ((double)tr * 1024.0 * (double)tc * 32.0);
+}
+
 bool env_is(const char *name, const char *value) {
     const char *e = getenv(name);
     return e && !strcmp(e, value);
@@ -38,8 +44,14 @@ bool env_is(const char *name, const char *value) {
 
 struct BackwardPlan {
     bool gw_slab, ga_slab;
+    bool gw_tall, ga_tall;  // slab kernel with the 1024 x 32 tile instead of 512 x 64
     int gw_splits;        // row-broadcast grad_w kernel: slabs of M
     size_t gw_scratch, ga_scratch;
+    // slab grad_w kernels read the activation codes from a transposed copy at[k][m] kept behind the partial
+    // sums in the scratch buffer (their row-code fetch is then coalesced; for a convolution it also
+    // replaces one implicit-im2col gather per column tile by a single one)
+    size_t gw_at_offset;  // bytes into the scratch buffer, a multiple of 16
+    int gw_at_pitch;      // 0 = no transposed copy
 };
 
 // Kernel choice for the two gradients.  Slab kernels amortise one slab build over 512 rows of the
@@ -56,15 +68,22 @@ BackwardPlan plan_backward(int bits, int M, int K, int N, int sms) {
     pl.ga_slab = bits >= 7 && N >= 384 && M >= 32 && slab_fill(N, M) >= 0.6;
     if (env_is("LUTGEMM_BACKWARD_KERNEL", "bcast")) pl.gw_slab = pl.ga_slab = false;
     if (env_is("LUTGEMM_BACKWARD_KERNEL", "slab")) pl.gw_slab = pl.ga_slab = true;
+    pl.gw_tall = pl.gw_slab && tall_fill(M, N) >= 0.85 * slab_fill(M, N);
+    pl.ga_tall = pl.ga_slab && tall_fill(N, M) >= 0.85 * slab_fill(N, M);
+    if (env_is("LUTGEMM_GRAD_TILE", "wide")) pl.gw_tall = pl.ga_tall = false;
+    if (env_is("LUTGEMM_GRAD_TILE", "tall")) { pl.gw_tall = pl.gw_slab; pl.ga_tall = pl.ga_slab; }
     pl.gw_splits = pl.gw_slab ? 1 : lutgemm::gw_num_splits(bits, M, K, N, sms);
     if (pl.gw_slab) {
-        const int rb = lutgemm::slab_f32_row_blocks(M);
+        const int rb = pl.gw_tall ? lutgemm::slab_tall_row_blocks(M) : lutgemm::slab_f32_row_blocks(M);
         pl.gw_scratch = rb > 1 ? (size_t)rb * K * N * sizeof(float) : 0;
+        pl.gw_at_offset = (pl.gw_scratch + 15) & ~(size_t)15;
+        pl.gw_at_pitch = (M + 15) & ~15;
+        pl.gw_scratch = pl.gw_at_offset + (size_t)pl.gw_at_pitch * K;
     } else {
         pl.gw_scratch = pl.gw_splits > 1 ? (size_t)pl.gw_splits * K * N * sizeof(float) : 0;
     }
     if (pl.ga_slab) {
-        const int rb = lutgemm::slab_f32_row_blocks(N);
+        const int rb = pl.ga_tall ? lutgemm::slab_tall_row_blocks(N) : lutgemm::slab_f32_row_blocks(N);
         pl.ga_scratch = rb > 1 ? (size_t)rb * K * M * sizeof(float) : 0;
     }
     return pl;
@@ -159,7 +178,7 @@ static int backward_impl(const float *gc, const uint8_t *a, const uint8_t *w, fl
     if (!gc || !a || !w || M <= 0 || K <= 0 || N <= 0) return LUTGEMM_E_BADARG;
     if ((ga && !lut_ga) || (gw && !lut_gw)) return LUTGEMM_E_BADARG;
     if ((reinterpret_cast<uintptr_t>(gc) & 3) || (reinterpret_cast<uintptr_t>(ga) & 3) ||
-        (reinterpret_cast<uintptr_t>(gw) & 3) || (reinterpret_cast<uintptr_t>(scratch) & 3) ||
+        (reinterpret_cast<uintptr_t>(gw) & 3) || (reinterpret_cast<uintptr_t>(scratch) & 15) ||
         (reinterpret_cast<uintptr_t>(lut_ga) & 1) || (reinterpret_cast<uintptr_t>(lut_gw) & 1))
         return LUTGEMM_E_BADARG;
     const int sms = current_num_sms();
@@ -171,15 +190,24 @@ static int backward_impl(const float *gc, const uint8_t *a, const uint8_t *w, fl
     if (gw) {
         // the weight gradient goes first: under data parallelism its all-reduce can then overlap gA
         if (pl.gw_scratch && (!scratch || scratch_bytes < pl.gw_scratch)) return LUTGEMM_E_SCRATCH;
+        const uint8_t *at = nullptr;
+        if (pl.gw_slab && pl.gw_at_pitch && !ws_impl) {
+            uint8_t *dst = static_cast<uint8_t *>(scratch) + pl.gw_at_offset;
+            const int trc = lutgemm::transpose_codes(a, dst, M, K, pl.gw_at_pitch, conv, s);
+            if (trc != LUTGEMM_OK) return trc;
+            at = dst;
+        }
         int rc = !pl.gw_slab ? lutgemm::backward_gw(gc, a, w, gw, lut_gw, bits, M, K, N, conv, sc, pl.gw_splits, sms, s)
                  : ws_impl   ? lutgemm::backward_gw_slab_ws(gc, a, w, gw, lut_gw, bits, M, K, N, sc, sms, s)
-                             : lutgemm::backward_gw_slab_f32(gc, a, w, gw, lut_gw, bits, M, K, N, conv, sc, sms, s);
+                 : pl.gw_tall ? lutgemm::backward_gw_slab_tall(gc, a, w, gw, lut_gw, bits, M, K, N, conv, sc, at, pl.gw_at_pitch, sms, s)
+                             : lutgemm::backward_gw_slab_f32(gc, a, w, gw, lut_gw, bits, M, K, N, conv, sc, at, pl.gw_at_pitch, sms, s);
         if (rc != LUTGEMM_OK) return rc;
     }
     if (ga) {
         if (pl.ga_scratch && (!scratch || scratch_bytes < pl.ga_scratch)) return LUTGEMM_E_SCRATCH;
         int rc = !pl.ga_slab ? lutgemm::backward_ga(gc, a, w, ga, lut_ga, bits, M, K, N, conv, sms, s)
                  : ws_impl   ? lutgemm::backward_ga_slab_ws(gc, a, w, ga, lut_ga, bits, M, K, N, sc, sms, s)
+                 : pl.ga_tall ? lutgemm::backward_ga_slab_tall(gc, a, w, ga, lut_ga, bits, M, K, N, conv, sc, sms, s)
                              : lutgemm::backward_ga_slab_f32(gc, a, w, ga, lut_ga, bits, M, K, N, conv, sc, sms, s);
         if (rc != LUTGEMM_OK) return rc;
     }
@@ -221,7 +249,7 @@ size_t lutgemm_conv2d_backward_scratch_bytes(int bits, int B, int C, int H, int 
     if (make_geom(B, C, H, W, kh, kw, stride, pad, dil, &g) != LUTGEMM_OK) return 0;
     const size_t M = (size_t)B * g.Ho * g.Wo, K = (size_t)C * kh * kw;
     // the unfolded activation gradient [B][K][Ho*Wo], then what the two gradient kernels need
-    return M * K * sizeof(float) + lutgemm_backward_scratch_bytes(bits, (int)M, (int)K, Cout);
+    return ((M * K * sizeof(float) + 15) & ~(size_t)15) + lutgemm_backward_scratch_bytes(bits, (int)M, (int)K, Cout);
 }
 
 int lutgemm_conv2d_backward(const float *gy, const uint8_t *x, const uint8_t *wmat, float *gx, float *gw,
@@ -232,7 +260,7 @@ int lutgemm_conv2d_backward(const float *gy, const uint8_t *x, const uint8_t *wm
     int rc = make_geom(B, C, H, W, kh, kw, stride, pad, dil, &g);
     if (rc != LUTGEMM_OK) return rc;
     const int M = B * g.Ho * g.Wo, K = C * kh * kw;
-    const size_t col_bytes = gx ? (size_t)M * K * sizeof(float) : 0;
+    const size_t col_bytes = gx ? (((size_t)M * K * sizeof(float) + 15) & ~(size_t)15) : 0;
     if (gx && (!scratch || scratch_bytes < col_bytes)) return LUTGEMM_E_SCRATCH;
     float *gcol = static_cast<float *>(scratch);
     void *rest = scratch ? static_cast<char *>(scratch) + col_bytes : nullptr;

@@ -466,6 +466,29 @@ __global__ void col2im_gather_kernel(const float *__restrict__ gcol, float *__re
     }
 }
 
+// at[k][m..m+3] per thread: lanes run over m, so the stores are coalesced; the byte loads of a plain [M,K]
+// matrix hit the same 32-byte sectors from the 32 k of a block, the unfolded image is read contiguously
+__global__ void __launch_bounds__(1024) transpose_codes_kernel(const uint8_t *__restrict__ a, uint8_t *__restrict__ at,
+                                                               int M, int K, int pitch, const ConvGeom conv) {
+    const int k = blockIdx.y * 32 + threadIdx.y;
+    const int m0 = (blockIdx.x * 32 + threadIdx.x) * 4;
+    if (k >= K || m0 >= pitch) return;
+    uint32_t v = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const int m = m0 + e;
+        if (m < M) v |= (conv.enabled ? conv_code(a, conv, m, k) : (uint32_t)a[(size_t)m * K + k]) << (8 * e);
+    }
+    *reinterpret_cast<uint32_t *>(at + (size_t)k * pitch + m0) = v;
+}
+
+int transpose_codes(const uint8_t *a, uint8_t *at, int M, int K, int pitch, const ConvGeom &conv, cudaStream_t stream) {
+    const dim3 block(32, 32), grid((pitch / 4 + 31) / 32, (K + 31) / 32);
+    if (grid.y > 65535u) return LUTGEMM_E_TOOLARGE;
+    transpose_codes_kernel<<<grid, block, 0, stream>>>(a, at, M, K, pitch, conv);
+    return cudaGetLastError() == cudaSuccess ? LUTGEMM_OK : LUTGEMM_E_CUDA;
+}
+
 int col2im_gather(const float *gcol, float *gx, const ConvGeom &g, cudaStream_t stream) {
     const long total = (long)g.B * g.C * g.H * g.W;
     const long blocks = (total + 255) / 256;

@@ -90,7 +90,14 @@ __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
     return v;
 }
 
-__device__ __forceinline__ uint32_t byte_of(uint32_t v, int i) { return (v >> (8 * i)) & 0xffu; }
+// byte i of v (one PRMT whatever i is; shift + mask costs two instructions for the middle bytes)
+__device__ __forceinline__ uint32_t byte_of(uint32_t v, int i) { return __byte_perm(v, 0u, 0x4440u + i); }
+// base + STRIDE * (byte i of v) in one integer dot-product instruction (STRIDE must fit a byte)
+template <int STRIDE>
+__device__ __forceinline__ uint32_t byte_scaled_add(uint32_t v, int i, uint32_t base) {
+    static_assert(STRIDE > 0 && STRIDE < 256, "stride must fit one byte of the dot-product operand");
+    return __dp4a(v, (uint32_t)STRIDE << (8 * i), base);
+}
 
 // Stage the padded wire-format table into shared memory as a dense [2^BITS][2^BITS] array of 16-bit
 // entries.  TRANSPOSE=false: dst[a][w]; TRANSPOSE=true: dst[w][a].  The reference copies the padded

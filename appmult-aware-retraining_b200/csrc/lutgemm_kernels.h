@@ -19,12 +19,22 @@ int forward_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t
 constexpr int kSlabF32Rows = 512;
 int slab_f32_row_blocks(int rdim);
 // gradient slab kernels with an fp32 slab (conversion done once per slab entry, in the build)
+// `at` (optional): the row codes transposed, at[k][m] with rows at_pitch bytes apart (transpose_codes)
 int backward_gw_slab_f32(const float *gc, const uint8_t *a, const uint8_t *w, float *gw, const int16_t *lut_gw,
-                         int bits, int M, int K, int N, const ConvGeom &conv, float *scratch, int num_sms,
-                         cudaStream_t stream);
+                         int bits, int M, int K, int N, const ConvGeom &conv, float *scratch, const uint8_t *at,
+                         int at_pitch, int num_sms, cudaStream_t stream);
 int backward_ga_slab_f32(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, const int16_t *lut_ga,
                          int bits, int M, int K, int N, const ConvGeom &conv, float *scratch, int num_sms,
                          cudaStream_t stream);
+// the same with a tall tile (1024 rows x 32 columns): half the slab-build work per look-up
+constexpr int kSlabTallRows = 1024;
+int slab_tall_row_blocks(int rdim);
+int backward_gw_slab_tall(const float *gc, const uint8_t *a, const uint8_t *w, float *gw, const int16_t *lut_gw,
+                          int bits, int M, int K, int N, const ConvGeom &conv, float *scratch, const uint8_t *at,
+                          int at_pitch, int num_sms, cudaStream_t stream);
+int backward_ga_slab_tall(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, const int16_t *lut_ga,
+                          int bits, int M, int K, int N, const ConvGeom &conv, float *scratch, int num_sms,
+                          cudaStream_t stream);
 // warp-specialised variants of the three slab kernels (producer warps build slabs, consumer warps gather)
 int forward_slab_ws(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K,
                     int N, int num_sms, cudaStream_t stream);
@@ -40,6 +50,10 @@ int slab_ws_bounded_wait_selftest(cudaStream_t stream);
 int slab_reduce_blocks(const float *part, float *out, int K, int C, int nblocks, bool transpose, int bkl_L,
                        int num_sms, cudaStream_t stream);
 
+
+// at[k][m] = a[m][k] (or the unfolded code image when conv.enabled); rows `pitch` bytes apart, pitch a multiple
+// of 16 and >= M, columns m >= M are written as 0
+int transpose_codes(const uint8_t *a, uint8_t *at, int M, int K, int pitch, const ConvGeom &conv, cudaStream_t stream);
 
 // gx[B,C,H,W] from the unfolded activation gradient gcol[B][C*kh*kw][Ho*Wo] (deterministic gather)
 int col2im_gather(const float *gcol, float *gx, const ConvGeom &g, cudaStream_t stream);

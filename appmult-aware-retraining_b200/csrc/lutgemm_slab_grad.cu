@@ -64,6 +64,8 @@ struct Args {
     int vec_a, vec_w, vec_g;
     ConvGeom conv;
     int ga_bkl;
+    const uint8_t *at;  // grad_w only, optional: transposed row codes at[k][m], rows at_pitch bytes apart
+    int at_pitch;       // a multiple of 16; columns m >= M hold 0
 };
 
 // PF = how many slab-row loads are kept in flight ahead of the FMAs that consume them.  Without explicit
@@ -135,7 +137,13 @@ __global__ void __launch_bounds__(32 * WARPS, 1) slab_grad_kernel(const Args p) 
     auto fetch_chunk = [&](int r0, int c0, int chunk) {
         const int kbase = chunk * KC;
         if (tid >= RT) return;
-        if (MODE == kGw) {
+        if (MODE == kGw && p.at) {
+            // row codes from the transposed copy at[k][m]: 16 rows per load, coalesced like the w operand
+            const int gk = kbase + tid / (RT / 16), gm = r0 + (tid % (RT / 16)) * 16;
+            prc = (gk < K && gm < p.at_pitch) ? *reinterpret_cast<const uint4 *>(p.at + (size_t)gk * p.at_pitch + gm)
+                                              : make_uint4(0, 0, 0, 0);
+            if (tid < KC * CT / 16) pcc = w_codes16(kbase + tid / (CT / 16), c0 + (tid % (CT / 16)) * 16);
+        } else if (MODE == kGw) {
             prc = a_codes16(r0 + tid, kbase);
             if (tid < KC * CT / 16) pcc = w_codes16(kbase + tid / (CT / 16), c0 + (tid % (CT / 16)) * 16);
         } else {
@@ -149,7 +157,13 @@ __global__ void __launch_bounds__(32 * WARPS, 1) slab_grad_kernel(const Args p) 
         uint8_t *cs = cc_s + stage * C::CC_STAGE;
         const uint32_t tr[4] = {prc.x & MASK4, prc.y & MASK4, prc.z & MASK4, prc.w & MASK4};
         const uint32_t tc[4] = {pcc.x & MASK4, pcc.y & MASK4, pcc.z & MASK4, pcc.w & MASK4};
-        if (MODE == kGw) {
+        if (MODE == kGw && p.at) {
+            *reinterpret_cast<uint4 *>(rs + (tid / (RT / 16)) * RT + (tid % (RT / 16)) * 16) =
+                make_uint4(tr[0], tr[1], tr[2], tr[3]);
+            if (tid < KC * CT / 16)
+                *reinterpret_cast<uint4 *>(cs + (tid / (CT / 16)) * CT + (tid % (CT / 16)) * 16) =
+                    make_uint4(tc[0], tc[1], tc[2], tc[3]);
+        } else if (MODE == kGw) {
 #pragma unroll
             for (int q = 0; q < 16; ++q) rs[q * RT + tid] = (uint8_t)(tr[q >> 2] >> (8 * (q & 3)));
             if (tid < KC * CT / 16)
@@ -299,18 +313,19 @@ __global__ void __launch_bounds__(32 * WARPS, 1) slab_grad_kernel(const Args p) 
                 const uint32_t ub = u_addr + (NBUF == 2 ? (k & 1) : 0) * C::U_BYTES + lane * 8;
                 float s0a = 0.f, s0b = 0.f, s1a = 0.f, s1b = 0.f;
                 float pf0[PF], pf1[PF];
+#define ROW_ADDR(v, i) (ub + byte_of(v, i) * (US * 4))
 #pragma unroll
                 for (int r = 0; r < PF; ++r) {
-                    const uint32_t x = byte_of(rv[r >> 2], r & 3);
-                    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(pf0[r]), "=f"(pf1[r]) : "r"(ub + x * (US * 4)));
+                    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];"
+                                 : "=f"(pf0[r]), "=f"(pf1[r]) : "r"(ROW_ADDR(rv[r >> 2], r & 3)));
                 }
 #pragma unroll
                 for (int r = 0; r < RW; ++r) {
                     const float f0 = pf0[r % PF], f1 = pf1[r % PF];
                     if (r + PF < RW) {
-                        const uint32_t x = byte_of(rv[(r + PF) >> 2], (r + PF) & 3);
                         asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];"
-                                     : "=f"(pf0[r % PF]), "=f"(pf1[r % PF]) : "r"(ub + x * (US * 4)));
+                                     : "=f"(pf0[r % PF]), "=f"(pf1[r % PF])
+                                     : "r"(ROW_ADDR(rv[(r + PF) >> 2], (r + PF) & 3)));
                     }
                     if (r & 1) { s0b = fmaf(f0, g[r][0], s0b); s1b = fmaf(f1, g[r][1], s1b); }
                     else       { s0a = fmaf(f0, g[r][0], s0a); s1a = fmaf(f1, g[r][1], s1a); }
@@ -385,8 +400,8 @@ int slab_reduce_blocks(const float *part, float *out, int K, int C, int nblocks,
 
 template <int BITS, int MODE, int WARPS, int RW, int PF>
 static int launch_slab_grad_w(const float *gc, const uint8_t *a, const uint8_t *w, float *out, const int16_t *lut,
-                            int M, int K, int N, const ConvGeom &conv, float *scratch, int num_sms,
-                            cudaStream_t stream) {
+                            int M, int K, int N, const ConvGeom &conv, float *scratch, const uint8_t *at,
+                            int at_pitch, int num_sms, cudaStream_t stream) {
     using C = sg::Cfg<BITS, WARPS, RW>;
     auto kern = sg::slab_grad_kernel<BITS, MODE, WARPS, RW, PF>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
@@ -395,6 +410,8 @@ static int launch_slab_grad_w(const float *gc, const uint8_t *a, const uint8_t *
     sg::Args p{};
     p.a = a; p.w = w; p.lut = lut; p.gc = gc; p.M = M; p.K = K; p.N = N;
     p.conv = conv;
+    p.at = MODE == sg::kGw ? at : nullptr;
+    p.at_pitch = at_pitch;
     p.ga_bkl = (MODE == sg::kGa && conv.enabled) ? 1 : 0;
     p.tiles_r = (RDIM + C::RT - 1) / C::RT;
     p.tiles_c = (CDIM + C::CT - 1) / C::CT;
@@ -430,19 +447,20 @@ static int launch_slab_grad_w(const float *gc, const uint8_t *a, const uint8_t *
 
 template <int BITS, int MODE>
 static int launch_slab_grad(const float *gc, const uint8_t *a, const uint8_t *w, float *out, const int16_t *lut,
-                            int M, int K, int N, const ConvGeom &conv, float *scratch, int num_sms,
-                            cudaStream_t stream) {
-    return launch_slab_grad_w<BITS, MODE, 16, 32, 4>(gc, a, w, out, lut, M, K, N, conv, scratch, num_sms, stream);
+                            int M, int K, int N, const ConvGeom &conv, float *scratch, const uint8_t *at,
+                            int at_pitch, int num_sms, cudaStream_t stream) {
+    return launch_slab_grad_w<BITS, MODE, 16, 32, 4>(gc, a, w, out, lut, M, K, N, conv, scratch, at, at_pitch, num_sms,
+                                                     stream);
 }
 
 int backward_gw_slab_f32(const float *gc, const uint8_t *a, const uint8_t *w, float *gw, const int16_t *lut_gw,
-                         int bits, int M, int K, int N, const ConvGeom &conv, float *scratch, int num_sms,
-                         cudaStream_t stream) {
+                         int bits, int M, int K, int N, const ConvGeom &conv, float *scratch, const uint8_t *at,
+                         int at_pitch, int num_sms, cudaStream_t stream) {
     switch (bits) {
-        case 4: return launch_slab_grad<4, sg::kGw>(gc, a, w, gw, lut_gw, M, K, N, conv, scratch, num_sms, stream);
-        case 6: return launch_slab_grad<6, sg::kGw>(gc, a, w, gw, lut_gw, M, K, N, conv, scratch, num_sms, stream);
-        case 7: return launch_slab_grad<7, sg::kGw>(gc, a, w, gw, lut_gw, M, K, N, conv, scratch, num_sms, stream);
-        case 8: return launch_slab_grad<8, sg::kGw>(gc, a, w, gw, lut_gw, M, K, N, conv, scratch, num_sms, stream);
+        case 4: return launch_slab_grad<4, sg::kGw>(gc, a, w, gw, lut_gw, M, K, N, conv, scratch, at, at_pitch, num_sms, stream);
+        case 6: return launch_slab_grad<6, sg::kGw>(gc, a, w, gw, lut_gw, M, K, N, conv, scratch, at, at_pitch, num_sms, stream);
+        case 7: return launch_slab_grad<7, sg::kGw>(gc, a, w, gw, lut_gw, M, K, N, conv, scratch, at, at_pitch, num_sms, stream);
+        case 8: return launch_slab_grad<8, sg::kGw>(gc, a, w, gw, lut_gw, M, K, N, conv, scratch, at, at_pitch, num_sms, stream);
     }
     return LUTGEMM_E_BITS;
 }
@@ -451,10 +469,10 @@ int backward_ga_slab_f32(const float *gc, const uint8_t *a, const uint8_t *w, fl
                          int bits, int M, int K, int N, const ConvGeom &conv, float *scratch, int num_sms,
                          cudaStream_t stream) {
     switch (bits) {
-        case 4: return launch_slab_grad<4, sg::kGa>(gc, a, w, ga, lut_ga, M, K, N, conv, scratch, num_sms, stream);
-        case 6: return launch_slab_grad<6, sg::kGa>(gc, a, w, ga, lut_ga, M, K, N, conv, scratch, num_sms, stream);
-        case 7: return launch_slab_grad<7, sg::kGa>(gc, a, w, ga, lut_ga, M, K, N, conv, scratch, num_sms, stream);
-        case 8: return launch_slab_grad<8, sg::kGa>(gc, a, w, ga, lut_ga, M, K, N, conv, scratch, num_sms, stream);
+        case 4: return launch_slab_grad<4, sg::kGa>(gc, a, w, ga, lut_ga, M, K, N, conv, scratch, nullptr, 0, num_sms, stream);
+        case 6: return launch_slab_grad<6, sg::kGa>(gc, a, w, ga, lut_ga, M, K, N, conv, scratch, nullptr, 0, num_sms, stream);
+        case 7: return launch_slab_grad<7, sg::kGa>(gc, a, w, ga, lut_ga, M, K, N, conv, scratch, nullptr, 0, num_sms, stream);
+        case 8: return launch_slab_grad<8, sg::kGa>(gc, a, w, ga, lut_ga, M, K, N, conv, scratch, nullptr, 0, num_sms, stream);
     }
     return LUTGEMM_E_BITS;
 }

@@ -59,7 +59,8 @@ int lutgemm_forward(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint1
 
 /*
  * Scratch bytes lutgemm_backward needs for a problem (0 when none is needed).  The weight-gradient
- * kernel splits its long reduction over M into slabs whose partial sums live in this buffer.
+ * kernel splits its long reduction over M into slabs whose partial sums live in this buffer, followed
+ * by a transposed copy of the activation codes.
  * No counterpart in the reference (its GB kernel never splits M, approx_gemm_backward.cu:587-608).
  */
 size_t lutgemm_backward_scratch_bytes(int bits, int M, int K, int N);
@@ -70,8 +71,8 @@ size_t lutgemm_backward_scratch_bytes(int bits, int M, int K, int N);
  *   gc [M,N] float32    ga [M,K] float32 (overwritten)    gw [K,N] float32 (overwritten)
  *   lut_ga, lut_gw flat int16 tables holding round(16 * dAM/da) and round(16 * dAM/dw)
  *   ga or gw may be NULL to skip that gradient.
- *   scratch: device buffer of at least lutgemm_backward_scratch_bytes() bytes (may be NULL when
- *   that is 0); its contents on return are unspecified.
+ *   scratch: device buffer of at least lutgemm_backward_scratch_bytes() bytes, 16-byte aligned (may be
+ *   NULL when that is 0); its contents on return are unspecified.
  * Replaces approx_gemm_backward_gpu, self_ops/src/approx_gemm_backward.cu:506-624 (kernels :13-258
  * and :261-492), bound to Python at self_ops/src/op_register.cpp:18.
  */

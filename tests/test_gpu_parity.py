@@ -109,15 +109,20 @@ def test_each_forward_kernel_on_every_shape_class(dev, oracle_c, bits, kernel, m
         assert np.array_equal(run_forward(dev, a, w, lf), oracle_c.forward(a, w, lf, bits)), (kernel, bits, M, K, N)
 
 
-@pytest.mark.parametrize("kernel", ["bcast", "slab-f32", "slab-ws"])
+@pytest.mark.parametrize("kernel", ["bcast", "slab-f32", "slab-tall", "slab-ws"])
 @pytest.mark.parametrize("bits", [4, 6, 7, 8])
 def test_each_backward_kernel_on_every_shape_class(dev, oracle_c, bits, kernel, monkeypatch):
-    """Every family of gradient kernels (LUTGEMM_BACKWARD_KERNEL / LUTGEMM_SLAB_IMPL: fp32 slab,
-    warp-specialised int16 slab, broadcast) on shapes of either class."""
+    """Every family of gradient kernels (LUTGEMM_BACKWARD_KERNEL / LUTGEMM_SLAB_IMPL / LUTGEMM_GRAD_TILE:
+    fp32 slab with the 512 x 64 and the 1024 x 32 tile, warp-specialised int16 slab, broadcast) on shapes
+    of either class."""
     monkeypatch.setenv("LUTGEMM_BACKWARD_KERNEL", kernel.split("-")[0])
-    monkeypatch.setenv("LUTGEMM_SLAB_IMPL", kernel.split("-")[1] if "-" in kernel else "f32")
+    monkeypatch.setenv("LUTGEMM_SLAB_IMPL", "ws" if kernel.endswith("-ws") else "f32")
+    monkeypatch.setenv("LUTGEMM_GRAD_TILE", "tall" if kernel.endswith("-tall") else "wide")
     _, la, lw = synth_wire(bits, seed=20 + bits)
-    for s, (M, K, N) in enumerate([(1, 1, 1), (5, 33, 3), (130, 16, 64), (515, 31, 67), (1024, 48, 128), (66, 35, 520)]):
+    shapes = [(1, 1, 1), (5, 33, 3), (130, 16, 64), (515, 31, 67), (1024, 48, 128), (66, 35, 520)]
+    if kernel.endswith("-tall"):
+        shapes += [(2100, 40, 70), (40, 57, 2050), (1030, 130, 1100)]
+    for s, (M, K, N) in enumerate(shapes):
         a, w, gc = rand_problem(bits, M, K, N, seed=11 * bits + s)
         ga, gw = run_backward(dev, gc, a, w, la, lw)
         check_backward(oracle_c, gc, a, w, la, lw, bits, ga, gw)
@@ -218,9 +223,14 @@ CONV_CASES = [  # B, Cin, H, W, Cout, k, stride, pad, dil
 
 
 @pytest.mark.parametrize("bits", [4, 6, 7, 8])
-def test_fused_conv_kernels_against_oracle(dev, oracle_c, bits):
-    """lutgemm_conv2d_forward / _backward (implicit im2col) against im2col + GEMM + col2im on the oracle."""
+@pytest.mark.parametrize("tile", ["auto", "tall"])
+def test_fused_conv_kernels_against_oracle(dev, oracle_c, bits, tile, monkeypatch):
+    """lutgemm_conv2d_forward / _backward (implicit im2col) against im2col + GEMM + col2im on the oracle;
+    once with the dispatcher's own choice and once with the tall-tile slab gradient kernels forced."""
     import approx_ops
+    if tile == "tall":
+        monkeypatch.setenv("LUTGEMM_BACKWARD_KERNEL", "slab")
+        monkeypatch.setenv("LUTGEMM_GRAD_TILE", "tall")
     lf, la, lw = synth_wire(bits, seed=30 + bits)
     lft, lat, lwt = (torch.from_numpy(t).to(dev) for t in (lf, la, lw))
     for s_, (B, Cin, H, W, Cout, k, st, p, d) in enumerate(CONV_CASES):

@@ -44,7 +44,7 @@ def test_no_alloc_weight_gradient_matches_regular_entry_point_twice_in_a_row():
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
     stream = torch.cuda.current_stream(dev).cuda_stream
-    # first a slab-path problem with eight 512-row blocks of partial sums, then a split-M problem of another
+    # first a slab-path problem with several row blocks of partial sums, then a split-M problem of another
     # shape: the second call finds the first call's partial sums in the array and must not be affected
     cases = [(8, 4096, 256, 320, 1), (6, 6000, 48, 64, 2), (8, 4096, 256, 320, 3)]
     for bits, M, K, N, seed in cases:
@@ -78,7 +78,7 @@ def test_no_alloc_entry_point_refuses_what_does_not_fit():
     lib.lutgemm_backward_gw_noalloc.restype = ci
     lib.lutgemm_backward_gw_noalloc.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, vp]
     dev = torch.device("cuda:0")
-    bits, M, K, N = 8, 8192, 1024, 1024  # sixteen 512-row blocks x 4 MiB of partial sums = 64 MiB > 32 MiB
+    bits, M, K, N = 8, 4096, 2048, 2048  # four 1024-row blocks x 16 MiB of partial sums = 64 MiB > 32 MiB
     a, w, gc, lw = _problem(dev, bits, M, K, N, 5)
     gw = torch.zeros(K, N, device=dev)
     rc = lib.lutgemm_backward_gw_noalloc(gc.data_ptr(), a.data_ptr(), w.data_ptr(), gw.data_ptr(), lw.data_ptr(),
