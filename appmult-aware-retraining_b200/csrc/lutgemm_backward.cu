@@ -37,14 +37,14 @@ struct GaCfg {
 };
 
 template <int BITS, int R, int C, int WM, int WK>
-__global__ void __launch_bounds__(32 * WM * WK, 1)
+__global__ void __launch_bounds__(32 * WM * WK, 2)
 ga_colbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, const uint8_t *__restrict__ w,
                    float *__restrict__ ga, const int16_t *__restrict__ lut, int M, int K, int N, int tiles_m,
                    int tiles_k, int vec_g, int vec_w, int vec_o, const ConvGeom conv) {
     using Cfg = GaCfg<BITS, R, C, WM, WK>;
     constexpr int MT = Cfg::MT, KT = Cfg::KT, NT = Cfg::NT, GS = Cfg::GSTRIDE, THREADS = Cfg::THREADS;
-    constexpr uint32_t MASK = Cfg::Q - 1;
-    static_assert(R % 4 == 0, "R k-columns per thread");
+    constexpr uint32_t MASK = Cfg::Q - 1, MASK4 = MASK * 0x01010101u;
+    static_assert(R % 4 == 0 && R <= 16, "R k-columns per thread");
 
     extern __shared__ __align__(16) uint8_t smem[];
     int16_t *lut_s = reinterpret_cast<int16_t *>(smem);
@@ -97,18 +97,29 @@ ga_colbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, 
         const int kth = k0 + wk * R;           // first k of this thread
         const int mth = m0 + wm * 32 * C + lane;  // first m of this thread; rows mth + 32*j
 
-        uint32_t aoff[R][C];
+        // activation codes of the thread's outputs, four k per register: the gather address is then
+        // row base + 2 * code in one integer dot-product instruction
+        uint32_t acode[R / 4][C];
         float acc[R][C];
 #pragma unroll
         for (int j = 0; j < C; ++j) {
             const int m = mth + 32 * j;
 #pragma unroll
-            for (int i = 0; i < R; ++i) {
-                const int k = kth + i;
-                uint32_t code = !(m < M && k < K) ? 0u : conv.enabled ? conv_code(a, conv, m, k) : a[(size_t)m * K + k];
-                aoff[i][j] = (code & MASK) * 2u;
-                acc[i][j] = 0.f;
+            for (int q = 0; q < R / 4; ++q) acode[q][j] = 0u;
+            if (m < M) {
+                if (conv.enabled) {
+                    const uint4 t = conv_code16(a, conv, m, kth, K);
+                    const uint32_t tw[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                    for (int q = 0; q < R / 4; ++q) acode[q][j] = tw[q] & MASK4;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < R; ++i)
+                        if (kth + i < K) acode[i >> 2][j] |= ((uint32_t)a[(size_t)m * K + kth + i] & MASK) << (8 * (i & 3));
+                }
             }
+#pragma unroll
+            for (int i = 0; i < R; ++i) acc[i][j] = 0.f;
         }
 
         load_tile(m0, k0, 0, 0);
@@ -134,7 +145,7 @@ ga_colbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, 
 #pragma unroll
                         for (int j = 0; j < C; ++j) {
                             const float g = nn == 0 ? g4[j].x : nn == 1 ? g4[j].y : nn == 2 ? g4[j].z : g4[j].w;
-                            acc[i][j] = fmaf(g, (float)lds_s16(wrow + aoff[i][j]), acc[i][j]);
+                            acc[i][j] = fmaf(g, (float)lds_s16(byte_scaled_add<2>(acode[i >> 2][j], i & 3, wrow)), acc[i][j]);
                         }
                     }
                 }
@@ -293,17 +304,20 @@ gw_rowbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, 
         auto col_of = [&](int j) { return C == 8 ? (j >> 2) * 128 + lane * 4 + (j & 3) : lane * C + j; };
         const int kth = k0 + wk * R, nth = n0 + wn * 32 * C;
 
-        uint32_t woff[R][C];
+        // weight codes of the thread's outputs, four k per register (gather address = row base + 2 * code)
+        uint32_t wcode[R / 4][C];
         float acc[R][C];
 #pragma unroll
-        for (int i = 0; i < R; ++i)
+        for (int j = 0; j < C; ++j) {
 #pragma unroll
-            for (int j = 0; j < C; ++j) {
+            for (int q = 0; q < R / 4; ++q) wcode[q][j] = 0u;
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
                 const int k = kth + i, n = nth + col_of(j);
-                uint32_t code = (k < K && n < N) ? w[(size_t)k * N + n] : 0u;
-                woff[i][j] = (code & MASK) * 2u;
+                if (k < K && n < N) wcode[i >> 2][j] |= ((uint32_t)w[(size_t)k * N + n] & MASK) << (8 * (i & 3));
                 acc[i][j] = 0.f;
             }
+        }
 
         const int nmt = (mend - mbeg + MT - 1) / MT;
         if (nmt > 0) load_tile(k0, n0, mbeg, mend, 0);
@@ -338,7 +352,7 @@ gw_rowbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, 
                     const uint32_t arow = lut_addr + ((byte_of(av[i / 4], i % 4) & MASK) << (BITS + 1));
 #pragma unroll
                     for (int j = 0; j < C; ++j)
-                        acc[i][j] = fmaf((float)lds_s16(arow + woff[i][j]), g[j], acc[i][j]);
+                        acc[i][j] = fmaf((float)lds_s16(byte_scaled_add<2>(wcode[i >> 2][j], i & 3, arow)), g[j], acc[i][j]);
                 }
             }
         }

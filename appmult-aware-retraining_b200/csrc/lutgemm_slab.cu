@@ -94,10 +94,6 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p) {
     auto fetch_chunk = [&](int m0, int n0, int chunk) {
         const int kbase = chunk * KC;
         const int m = min(m0 + tid, M - 1);
-#ifdef LUTGEMM_FWD_AT_EXPERIMENT
-        if (true) prc = *reinterpret_cast<const uint4 *>(p.a + (size_t)min(kbase + tid / 32, K - 1) * M + m0 + (tid % 32) * 16);
-        else
-#endif
         if (kbase >= K) prc = make_uint4(0, 0, 0, 0);
         else if (p.conv.enabled) prc = conv_code16(p.a, p.conv, m, kbase, K);
         else if (p.vec_a) prc = *reinterpret_cast<const uint4 *>(p.a + (size_t)m * K + kbase);
@@ -113,12 +109,8 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p) {
         // codes are masked to BITS bits here, once, so no stray code can index outside a slab or the table
         const uint32_t tr[4] = {prc.x & MASK4, prc.y & MASK4, prc.z & MASK4, prc.w & MASK4};
         uint8_t *rs = rc_s + stage * C::RC_STAGE;
-#ifdef LUTGEMM_FWD_AT_EXPERIMENT
-        *reinterpret_cast<uint4 *>(rs + (tid / 32) * RT + (tid % 32) * 16) = make_uint4(tr[0], tr[1], tr[2], tr[3]);
-#else
 #pragma unroll
         for (int q = 0; q < 16; ++q) rs[q * RT + tid] = (uint8_t)(tr[q >> 2] >> (8 * (q & 3)));
-#endif
         if (tid < KC * CT / 16)
             *reinterpret_cast<uint4 *>(cc_s + stage * C::CC_STAGE + (tid / (CT / 16)) * CT + (tid % (CT / 16)) * 16) =
                 make_uint4(pcc.x & MASK4, pcc.y & MASK4, pcc.z & MASK4, pcc.w & MASK4);
