@@ -56,6 +56,13 @@ def _load():
     lib.lutgemm_conv2d_backward_scratch_bytes.argtypes = [ci] * 11
     lib.lutgemm_conv2d_backward.restype = ci
     lib.lutgemm_conv2d_backward.argtypes = [vp] * 7 + [ci] * 11 + [vp, sz, vp]
+    cf = ctypes.c_float
+    lib.lutgemm_quantize_activations.restype = ci
+    lib.lutgemm_quantize_activations.argtypes = [vp, cl, cl, cl, cl, ci, ci, ci, ci, vp, vp, cf, vp, vp, vp]
+    lib.lutgemm_quantize_activations_backward.restype = ci
+    lib.lutgemm_quantize_activations_backward.argtypes = [vp, cl, cl, cl, cl, ci, ci, ci, ci, vp, vp, cf, vp, vp, vp, vp, vp, vp]
+    lib.lutgemm_conv2d_epilogue.restype = ci
+    lib.lutgemm_conv2d_epilogue.argtypes = [vp] * 10 + [cl, ci, ci, vp]
     lib.lutgemm_device_error.restype = ci
     lib.lutgemm_device_error.argtypes = [ctypes.POINTER(ci)]
     lib.lutgemm_selftest_bounded_wait.restype = ci
@@ -261,3 +268,73 @@ def approx_conv2d_backward(gy: torch.Tensor, x: torch.Tensor, wmat: torch.Tensor
                                          lut_grad_a.data_ptr(), lut_grad_b.data_ptr(), bits, B, C, H, W, Cout, kh, kw,
                                          stride, pad, dil, scratch.data_ptr(), nbytes, _stream_ptr(dev))
     _check(rc, "approx_conv2d_backward")
+
+
+def _dense_4d(x: torch.Tensor, name: str) -> None:
+    if not x.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if x.dtype != torch.float32 or x.dim() != 4:
+        raise RuntimeError(f"{name} must be a 4-D float32 tensor")
+    if not (x.is_contiguous() or x.is_contiguous(memory_format=torch.channels_last)):
+        raise RuntimeError(f"{name} must be dense (NCHW or channels-last)")
+
+
+def quantize_activations(x: torch.Tensor, scale: torch.Tensor, zp_neg: torch.Tensor, qmax: float,
+                         want_chansum: bool = True):
+    """codes = uint8(clamp(round(x / scale - zp_neg), 0, qmax)), NCHW-contiguous, and (optionally) their sums over
+    the channels [B, H, W]; one pass over x in whichever dense layout it has.  scale / zp_neg: 1-element device
+    tensors."""
+    _dense_4d(x, "input_tensor")
+    B, C, H, W = x.shape
+    codes = torch.empty((B, C, H, W), dtype=torch.uint8, device=x.device)
+    chansum = torch.zeros((B, H, W), dtype=torch.float32, device=x.device) if want_chansum else None
+    sb, sc, sh, sw = x.stride()
+    with torch.cuda.device(x.device):
+        rc = _load().lutgemm_quantize_activations(x.data_ptr(), sb, sc, sh, sw, B, C, H, W, scale.data_ptr(),
+                                                  zp_neg.data_ptr(), float(qmax), codes.data_ptr(),
+                                                  chansum.data_ptr() if want_chansum else None, _stream_ptr(x.device))
+    _check(rc, "quantize_activations")
+    return codes, chansum
+
+
+def quantize_activations_backward(x: torch.Tensor, scale: torch.Tensor, zp_neg: torch.Tensor, qmax: float,
+                                  gcodes: torch.Tensor, box_t, s_w: torch.Tensor, z_w: torch.Tensor) -> torch.Tensor:
+    """Gradient w.r.t. x of the quantised layer input (clamp mask, straight-through rounding), in the layout of x:
+    mask * s_w * (gcodes + z_w * box_t).  gcodes: f32 NCHW-contiguous; box_t: f32 [B, H, W] or None."""
+    _dense_4d(x, "input_tensor")
+    _check_input(gcodes, torch.float32, "grad_codes_tensor")
+    if tuple(gcodes.shape) != tuple(x.shape):
+        raise RuntimeError("grad_codes_tensor must have the shape of input_tensor")
+    B, C, H, W = x.shape
+    gx = torch.empty_like(x)  # preserves the (dense) strides of x
+    sb, sc, sh, sw = x.stride()
+    if gx.stride() != x.stride():
+        raise RuntimeError("could not allocate a gradient with the strides of input_tensor")
+    if box_t is not None:
+        _check_input(box_t, torch.float32, "box_t_tensor")
+    with torch.cuda.device(x.device):
+        rc = _load().lutgemm_quantize_activations_backward(
+            x.data_ptr(), sb, sc, sh, sw, B, C, H, W, scale.data_ptr(), zp_neg.data_ptr(), float(qmax), gcodes.data_ptr(),
+            box_t.data_ptr() if box_t is not None else None, s_w.data_ptr(), z_w.data_ptr(), gx.data_ptr(),
+            _stream_ptr(x.device))
+    _check(rc, "quantize_activations_backward")
+    return gx
+
+
+def conv2d_epilogue(y: torch.Tensor, box: torch.Tensor, sumw_t: torch.Tensor, taps: torch.Tensor, s_a: torch.Tensor,
+                    s_w: torch.Tensor, z_a: torch.Tensor, z_w: torch.Tensor, bias, L: int) -> torch.Tensor:
+    """out[m, co] = s_a s_w (y + z_w box[m] + z_a sumw_t[l, co] + z_a z_w taps[l]) (+ bias[co]);  y: u32 [M, Cout]."""
+    _check_input(y, torch.uint32, "accumulator_tensor")
+    M, Cout = y.shape
+    for t, shape, name in ((box, (M,), "box"), (sumw_t, (L, Cout), "sumw_t"), (taps, (L,), "taps")):
+        _check_input(t, torch.float32, name)
+        if tuple(t.shape) != shape:
+            raise RuntimeError(f"{name} has shape {tuple(t.shape)}, expected {shape}")
+    out = torch.empty((M, Cout), dtype=torch.float32, device=y.device)
+    with torch.cuda.device(y.device):
+        rc = _load().lutgemm_conv2d_epilogue(y.data_ptr(), box.data_ptr(), sumw_t.data_ptr(), taps.data_ptr(),
+                                             s_a.data_ptr(), s_w.data_ptr(), z_a.data_ptr(), z_w.data_ptr(),
+                                             bias.data_ptr() if bias is not None else None, out.data_ptr(), M, L, Cout,
+                                             _stream_ptr(y.device))
+    _check(rc, "conv2d_epilogue")
+    return out

@@ -65,7 +65,7 @@ BackwardPlan plan_backward(int bits, int M, int K, int N, int sms) {
     // where the broadcast gathers suffer bank conflicts (7 and 8 bits); at 4 and 6 bits a table row is
     // conflict-free already
     pl.gw_slab = bits >= 7 && M >= 512 && N >= 32 && slab_fill(M, N) >= 0.6;
-    pl.ga_slab = bits >= 7 && N >= 384 && M >= 32 && slab_fill(N, M) >= 0.6;
+    pl.ga_slab = bits >= 7 && N >= 768 && M >= 32 && slab_fill(N, M) >= 0.6;
     if (env_is("LUTGEMM_BACKWARD_KERNEL", "bcast")) pl.gw_slab = pl.ga_slab = false;
     if (env_is("LUTGEMM_BACKWARD_KERNEL", "slab")) pl.gw_slab = pl.ga_slab = true;
     pl.gw_tall = pl.gw_slab && tall_fill(M, N) >= 0.85 * slab_fill(M, N);
@@ -269,6 +269,41 @@ int lutgemm_conv2d_backward(const float *gy, const uint8_t *x, const uint8_t *wm
     if (rc != LUTGEMM_OK) return rc;
     if (gx) return lutgemm::col2im_gather(gcol, gx, g, static_cast<cudaStream_t>(stream));
     return LUTGEMM_OK;
+}
+
+// ---- layer prologue / epilogue ---------------------------------------------------------------------------
+int lutgemm_quantize_activations(const float *x, long stride_b, long stride_c, long stride_h, long stride_w, int B,
+                                 int C, int H, int W, const float *scale, const float *zp_neg, float qmax,
+                                 uint8_t *codes, float *chansum, void *stream) {
+    if (!x || !scale || !zp_neg || !codes || B <= 0 || C <= 0 || H <= 0 || W <= 0 || !(qmax >= 1.f && qmax <= 255.f))
+        return LUTGEMM_E_BADARG;
+    const int sms = current_num_sms();
+    if (sms <= 0) return LUTGEMM_E_CUDA;
+    return lutgemm::quantize_codes(x, stride_b, stride_c, stride_h, stride_w, B, C, H, W, scale, zp_neg, qmax, codes,
+                                   chansum, sms, static_cast<cudaStream_t>(stream));
+}
+
+int lutgemm_quantize_activations_backward(const float *x, long stride_b, long stride_c, long stride_h, long stride_w,
+                                          int B, int C, int H, int W, const float *scale, const float *zp_neg,
+                                          float qmax, const float *gcodes, const float *box_t, const float *s_w,
+                                          const float *z_w, float *gx, void *stream) {
+    if (!x || !scale || !zp_neg || !gcodes || !s_w || !z_w || !gx || B <= 0 || C <= 0 || H <= 0 || W <= 0)
+        return LUTGEMM_E_BADARG;
+    const int sms = current_num_sms();
+    if (sms <= 0) return LUTGEMM_E_CUDA;
+    return lutgemm::quantize_backward(x, stride_b, stride_c, stride_h, stride_w, B, C, H, W, scale, zp_neg, qmax, gcodes,
+                                      box_t, s_w, z_w, gx, sms, static_cast<cudaStream_t>(stream));
+}
+
+int lutgemm_conv2d_epilogue(const uint32_t *y, const float *box, const float *sumw_t, const float *taps,
+                            const float *s_a, const float *s_w, const float *z_a, const float *z_w, const float *bias,
+                            float *out, long M, int L, int Cout, void *stream) {
+    if (!y || !box || !sumw_t || !taps || !s_a || !s_w || !z_a || !z_w || !out || M <= 0 || L <= 0 || Cout <= 0)
+        return LUTGEMM_E_BADARG;
+    const int sms = current_num_sms();
+    if (sms <= 0) return LUTGEMM_E_CUDA;
+    return lutgemm::conv_epilogue(y, box, sumw_t, taps, s_a, s_w, z_a, z_w, bias, out, M, L, Cout, sms,
+                                  static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

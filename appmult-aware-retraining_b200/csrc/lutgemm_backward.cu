@@ -37,7 +37,7 @@ struct GaCfg {
 };
 
 template <int BITS, int R, int C, int WM, int WK>
-__global__ void __launch_bounds__(32 * WM * WK, 2)
+__global__ void __launch_bounds__(32 * WM * WK, WM * WK <= 8 ? 2 : 1)
 ga_colbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, const uint8_t *__restrict__ w,
                    float *__restrict__ ga, const int16_t *__restrict__ lut, int M, int K, int N, int tiles_m,
                    int tiles_k, int vec_g, int vec_w, int vec_o, const ConvGeom conv) {
@@ -209,7 +209,8 @@ int backward_ga(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, 
         case 4: return launch_ga<4, 8, 4, 2, 4>(gc, a, w, ga, lut_ga, M, K, N, conv, num_sms, stream);
         case 6: return launch_ga<6, 8, 4, 2, 4>(gc, a, w, ga, lut_ga, M, K, N, conv, num_sms, stream);
         case 7: return launch_ga<7, 8, 4, 2, 4>(gc, a, w, ga, lut_ga, M, K, N, conv, num_sms, stream);
-        case 8: return launch_ga<8, 8, 4, 2, 4>(gc, a, w, ga, lut_ga, M, K, N, conv, num_sms, stream);
+        // the 128 KB table leaves room for one CTA per SM only: make it 16 warps
+        case 8: return launch_ga<8, 8, 4, 4, 4>(gc, a, w, ga, lut_ga, M, K, N, conv, num_sms, stream);
     }
     return LUTGEMM_E_BITS;
 }
@@ -453,61 +454,100 @@ int backward_gw(const float *gc, const uint8_t *a, const uint8_t *w, float *gw, 
 // consecutive threads read consecutive ow of the same gcol row.  Adjoint of the implicit im2col above
 // (the reference gets it from autograd of F.unfold / F.pad, self_ops/ops_py/approx_ops.py:556-563).
 // ------------------------------------------------------------------------------------------------
-__global__ void col2im_gather_kernel(const float *__restrict__ gcol, float *__restrict__ gx, const ConvGeom g) {
-    const long total = (long)g.B * g.C * g.H * g.W;
+template <bool STRIDE1>
+__global__ void __launch_bounds__(256) col2im_gather_kernel(const float *__restrict__ gcol, float *__restrict__ gx,
+                                                            const ConvGeom g) {
+    // one thread per four consecutive w of an input row (b, c, h)
+    const int W4 = (g.W + 3) / 4;
+    const long total = (long)g.B * g.C * g.H * W4;
     const int L = g.Ho * g.Wo, K = g.C * g.kh * g.kw;
     for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
-        const int w = (int)(idx % g.W);
-        const int h = (int)((idx / g.W) % g.H);
-        const int c = (int)((idx / ((long)g.W * g.H)) % g.C);
-        const int b = (int)(idx / ((long)g.W * g.H * g.C));
+        const int w0 = (int)(idx % W4) * 4;
+        const long row_id = idx / W4;           // (b * C + c) * H + h
+        const int h = (int)(row_id % g.H);
+        const int bc = (int)(row_id / g.H);
+        const int c = bc % g.C, b = bc / g.C;
         const float *base = gcol + ((size_t)b * K + (size_t)c * g.kh * g.kw) * L;
-        float s = 0.f;
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
         for (int i = 0; i < g.kh; ++i) {
             const int th = h + g.pad - i * g.dil;
-            if (th < 0 || th % g.stride) continue;
-            const int oh = th / g.stride;
+            if (th < 0) continue;
+            int oh = th;
+            if (!STRIDE1) {
+                if (th % g.stride) continue;
+                oh = th / g.stride;
+            }
             if (oh >= g.Ho) continue;
+            const float *row = base + (size_t)(i * g.kw) * L + (size_t)oh * g.Wo;
             for (int j = 0; j < g.kw; ++j) {
-                const int tw = w + g.pad - j * g.dil;
-                if (tw < 0 || tw % g.stride) continue;
-                const int ow = tw / g.stride;
-                if (ow >= g.Wo) continue;
-                s += base[(size_t)(i * g.kw + j) * L + oh * g.Wo + ow];
+                const float *rj = row + (size_t)j * L;
+                const int tw0 = w0 + g.pad - j * g.dil;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int tw = tw0 + e;
+                    int ow = tw;
+                    bool ok = tw >= 0 && w0 + e < g.W;
+                    if (!STRIDE1) {
+                        ok = ok && (tw % g.stride == 0);
+                        ow = tw / g.stride;
+                    }
+                    if (ok && ow < g.Wo) s[e] += rj[ow];
+                }
             }
         }
-        gx[idx] = s;
+        float *dst = gx + row_id * g.W + w0;
+        if (w0 + 3 < g.W && (g.W & 3) == 0 && (reinterpret_cast<uintptr_t>(gx) & 15) == 0) {
+            *reinterpret_cast<float4 *>(dst) = make_float4(s[0], s[1], s[2], s[3]);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (w0 + e < g.W) dst[e] = s[e];
+        }
     }
 }
 
-// at[k][m..m+3] per thread: lanes run over m, so the stores are coalesced; the byte loads of a plain [M,K]
-// matrix hit the same 32-byte sectors from the 32 k of a block, the unfolded image is read contiguously
+// at[k][m..m+15] per thread: lanes run over m, so the 16-byte stores are coalesced.  For the unfolded code
+// image the (channel, tap) of k and the (image, row, column) of the first m are decoded once per thread and m
+// advances incrementally; for a plain [M,K] matrix the byte loads of the 32 k of a block share sectors.
 __global__ void __launch_bounds__(1024) transpose_codes_kernel(const uint8_t *__restrict__ a, uint8_t *__restrict__ at,
-                                                               int M, int K, int pitch, const ConvGeom conv) {
+                                                               int M, int K, int pitch, const ConvGeom g) {
     const int k = blockIdx.y * 32 + threadIdx.y;
-    const int m0 = (blockIdx.x * 32 + threadIdx.x) * 4;
+    const int m0 = (blockIdx.x * 32 + threadIdx.x) * 16;
     if (k >= K || m0 >= pitch) return;
-    uint32_t v = 0;
+    uint32_t v[4] = {0u, 0u, 0u, 0u};
+    if (g.enabled) {
+        const int L = g.Ho * g.Wo, kk = g.kh * g.kw;
+        const int c = k / kk, r = k - c * kk, i = r / g.kw, j = r - i * g.kw;
+        int b = m0 / L, l = m0 - b * L, oh = l / g.Wo, ow = l - oh * g.Wo;
+        const int dh = i * g.dil - g.pad, dw = j * g.dil - g.pad;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-        const int m = m0 + e;
-        if (m < M) v |= (conv.enabled ? conv_code(a, conv, m, k) : (uint32_t)a[(size_t)m * K + k]) << (8 * e);
+        for (int e = 0; e < 16; ++e) {
+            const int ih = oh * g.stride + dh, iw = ow * g.stride + dw;
+            if (m0 + e < M && (unsigned)ih < (unsigned)g.H && (unsigned)iw < (unsigned)g.W)
+                v[e >> 2] |= (uint32_t)a[((size_t)(b * g.C + c) * g.H + ih) * g.W + iw] << (8 * (e & 3));
+            if (++ow == g.Wo) { ow = 0; if (++oh == g.Ho) { oh = 0; ++b; } }
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e)
+            if (m0 + e < M) v[e >> 2] |= (uint32_t)a[(size_t)(m0 + e) * K + k] << (8 * (e & 3));
     }
-    *reinterpret_cast<uint32_t *>(at + (size_t)k * pitch + m0) = v;
+    *reinterpret_cast<uint4 *>(at + (size_t)k * pitch + m0) = make_uint4(v[0], v[1], v[2], v[3]);
 }
 
 int transpose_codes(const uint8_t *a, uint8_t *at, int M, int K, int pitch, const ConvGeom &conv, cudaStream_t stream) {
-    const dim3 block(32, 32), grid((pitch / 4 + 31) / 32, (K + 31) / 32);
+    const dim3 block(32, 32), grid((pitch / 16 + 31) / 32, (K + 31) / 32);
     if (grid.y > 65535u) return LUTGEMM_E_TOOLARGE;
     transpose_codes_kernel<<<grid, block, 0, stream>>>(a, at, M, K, pitch, conv);
     return cudaGetLastError() == cudaSuccess ? LUTGEMM_OK : LUTGEMM_E_CUDA;
 }
 
 int col2im_gather(const float *gcol, float *gx, const ConvGeom &g, cudaStream_t stream) {
-    const long total = (long)g.B * g.C * g.H * g.W;
+    const long total = (long)g.B * g.C * g.H * ((g.W + 3) / 4);
     const long blocks = (total + 255) / 256;
-    const int grid = (int)(blocks < 148L * 16 ? blocks : 148L * 16);
-    col2im_gather_kernel<<<grid, 256, 0, stream>>>(gcol, gx, g);
+    const int grid = (int)(blocks < 148L * 32 ? blocks : 148L * 32);
+    if (g.stride == 1) col2im_gather_kernel<true><<<grid, 256, 0, stream>>>(gcol, gx, g);
+    else col2im_gather_kernel<false><<<grid, 256, 0, stream>>>(gcol, gx, g);
     return cudaGetLastError() == cudaSuccess ? LUTGEMM_OK : LUTGEMM_E_CUDA;
 }
 

@@ -58,6 +58,16 @@ int transpose_codes(const uint8_t *a, uint8_t *at, int M, int K, int pitch, cons
 // gx[B,C,H,W] from the unfolded activation gradient gcol[B][C*kh*kw][Ho*Wo] (deterministic gather)
 int col2im_gather(const float *gcol, float *gx, const ConvGeom &g, cudaStream_t stream);
 
+// quantisation prologue / epilogue of an approximate convolution layer (lutgemm_quant.cu); strides in elements
+int quantize_codes(const float *x, long sb, long sc, long sh, long sw, int B, int C, int H, int W, const float *scale,
+                   const float *zp_neg, float qmax, uint8_t *codes, float *chansum, int num_sms, cudaStream_t stream);
+int quantize_backward(const float *x, long sb, long sc, long sh, long sw, int B, int C, int H, int W, const float *scale,
+                      const float *zp_neg, float qmax, const float *gcodes, const float *boxT, const float *s_w,
+                      const float *z_w, float *gx, int num_sms, cudaStream_t stream);
+int conv_epilogue(const uint32_t *y, const float *box, const float *sumw_t, const float *taps, const float *s_a,
+                  const float *s_w, const float *z_a, const float *z_w, const float *bias, float *out, long M, int L,
+                  int Cout, int num_sms, cudaStream_t stream);
+
 // number of slabs the weight-gradient kernel splits M into (1 = no scratch needed)
 int gw_num_splits(int bits, int M, int K, int N, int num_sms);
 

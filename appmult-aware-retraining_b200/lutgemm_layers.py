@@ -15,7 +15,8 @@ box filter of the channel-summed codes, one batch-independent convolution of a o
 weight codes, a tap count) instead of three full convolutions - identical in exact arithmetic; linear
 layers go through the approximate multiplier too (`AppLinear`), which the reference's `QuantLinear`
 (:78-113) does not do; the convolution can use the fused implicit-im2col kernels instead of
-`F.unfold`.  Spatial padding is code 0 and therefore contributes LUT[0][w], as in the reference
+`F.unfold` (conv_impl="fused"), and the whole layer - quantisation, convolution, cross terms, scaling - can
+run as three kernels in the forward pass (conv_impl="layer").  Spatial padding is code 0 and therefore contributes LUT[0][w], as in the reference
 (self_ops/ops_py/approx_ops.py:556)."""
 from __future__ import annotations
 
@@ -23,7 +24,123 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+import approx_ops
 import self_ops
+from self_ops.ops_py import approx_ops as _ops_state
+
+
+def _out_hw(H, W, kh, kw, stride, pad, dil):
+    return (H + 2 * pad - dil * (kh - 1) - 1) // stride + 1, (W + 2 * pad - dil * (kw - 1) - 1) // stride + 1
+
+
+# The zero-point cross terms are window sums.  They are evaluated with slices and small fp32 matrix products
+# rather than library convolutions, which may round their inputs to TF32 (channel sums of codes need 16 bits).
+def _tap_slices(geom):
+    H, W, kh, kw, stride, pad, dil = geom
+    Ho, Wo = _out_hw(H, W, kh, kw, stride, pad, dil)
+    for i in range(kh):
+        for j in range(kw):
+            yield (slice(i * dil, i * dil + (Ho - 1) * stride + 1, stride),
+                   slice(j * dil, j * dil + (Wo - 1) * stride + 1, stride))
+
+
+def _window_sum(img, geom):
+    """[B, H, W] -> [B, Ho, Wo]: sum of the kernel window at every output position (zero padding)."""
+    pad = geom[5]
+    padded = F.pad(img, (pad, pad, pad, pad))
+    out = None
+    for sh, sw in _tap_slices(geom):
+        out = padded[:, sh, sw].clone() if out is None else out.add_(padded[:, sh, sw])
+    return out
+
+
+def _window_sum_adjoint(g, geom):
+    """[B, Ho, Wo] -> [B, H, W]: adjoint of `_window_sum`."""
+    H, W, pad = geom[0], geom[1], geom[5]
+    padded = torch.zeros(g.shape[0], H + 2 * pad, W + 2 * pad, dtype=g.dtype, device=g.device)
+    for sh, sw in _tap_slices(geom):
+        padded[:, sh, sw] += g
+    return padded[:, pad:pad + H, pad:pad + W].contiguous()
+
+
+_VALID_TAPS = {}
+
+
+def _valid_taps(geom, device):
+    """[kh*kw, Ho*Wo] fp32: 1 where tap (i, j) of output position l falls inside the image (geometry only)."""
+    key = (geom, str(device))
+    if key not in _VALID_TAPS:
+        H, W, kh, kw, stride, pad, dil = geom
+        padded = F.pad(torch.ones(1, H, W, device=device), (pad, pad, pad, pad))
+        _VALID_TAPS[key] = torch.stack([padded[0, sh, sw].reshape(-1) for sh, sw in _tap_slices(geom)]).contiguous()
+    return _VALID_TAPS[key]
+
+
+class _AppConvLayer(torch.autograd.Function):
+    """The whole approximate convolution layer around the fused implicit-im2col kernels: quantisation prologue
+    (one pass over the activations, any dense layout), LUT convolution, de-quantisation epilogue with the three
+    zero-point cross terms (one pass over the accumulators); backward: LUT gradients on the un-scaled grad_out,
+    then one pass that applies clamp mask, weight scale and the cross-term gradient in the layout of the input.
+    Same values and gradients as the expression in `AppConv2d.forward` evaluated by autograd."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, quant, a_qmax, w_qmax, stride, padding, dilation):
+        # quant = [s_a, z_a, s_w, z_w] (one device tensor, so nothing here synchronises with the host)
+        if _ops_state.lut_appmult is None:
+            raise RuntimeError("lookup tables are not initialised: call init_lookup_tables first")
+        s_a, z_a, s_w, z_w = (quant[i:i + 1] for i in range(4))
+        B, Cin, H, W = x.shape
+        Cout, _, kh, kw = weight.shape
+        Ho, Wo = _out_hw(H, W, kh, kw, stride, padding, dilation)
+        L, M = Ho * Wo, B * Ho * Wo
+        if not (x.is_contiguous() or x.is_contiguous(memory_format=torch.channels_last)):
+            x = x.contiguous()
+        codes, chansum = approx_ops.quantize_activations(x, s_a, z_a, a_qmax)
+        qw = torch.clamp(torch.round(weight / s_w - z_w), 0.0, w_qmax)
+        wmat = qw.reshape(Cout, -1).t().to(torch.uint8).contiguous()
+        y = torch.empty((M, Cout), dtype=torch.uint32, device=x.device)
+        approx_ops.approx_conv2d_forward(codes, wmat, y, _ops_state.lut_appmult, kh, kw, stride, padding, dilation)
+        geom = (H, W, kh, kw, stride, padding, dilation)
+        valid = _valid_taps(geom, x.device)                                   # [kh*kw, L]
+        box = _window_sum(chansum, geom).reshape(M)
+        sumw_t = (valid.t() @ qw.sum(dim=1).reshape(Cout, kh * kw).t()).contiguous()  # [L, Cout]
+        taps = valid.sum(dim=0) * float(Cin)
+        out = approx_ops.conv2d_epilogue(y, box, sumw_t, taps, s_a, s_w, z_a, z_w, bias, L)
+        ctx.save_for_backward(x, codes, wmat, weight, quant)
+        ctx.cfg = (a_qmax, w_qmax, stride, padding, dilation, Ho, Wo, bias is not None)
+        return out.view(B, Ho, Wo, Cout).permute(0, 3, 1, 2)  # NCHW view of channels-last memory
+
+    @staticmethod
+    def backward(ctx, g_out):
+        x, codes, wmat, weight, quant = ctx.saved_tensors
+        a_qmax, w_qmax, stride, padding, dilation, Ho, Wo, has_bias = ctx.cfg
+        s_a, z_a, s_w, z_w = (quant[i:i + 1] for i in range(4))
+        B, Cin, H, W = x.shape
+        Cout, _, kh, kw = weight.shape
+        L, M = Ho * Wo, B * Ho * Wo
+        gy = g_out.permute(0, 2, 3, 1).reshape(M, Cout).contiguous()  # a view when g_out is channels-last
+        need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        gcodes = torch.empty(codes.shape, dtype=torch.float32, device=gy.device) if need_x else None
+        gwmat = torch.empty(wmat.shape, dtype=torch.float32, device=gy.device) if need_w else None
+        if need_x or need_w:
+            approx_ops.approx_conv2d_backward(gy, codes, wmat, gcodes, gwmat, _ops_state.lut_grad_a, _ops_state.lut_grad_b,
+                                              kh, kw, stride, padding, dilation)
+        geom = (H, W, kh, kw, stride, padding, dilation)
+        gx = gw = gb = None
+        if need_x:
+            # cross term z_w * box(q_a): its adjoint spreads the channel sum of grad_out over each window
+            box_t = _window_sum_adjoint(gy.sum(dim=1).view(B, Ho, Wo), geom)
+            gx = approx_ops.quantize_activations_backward(x, s_a, z_a, a_qmax, gcodes, box_t, s_w, z_w)
+        if need_w:
+            # cross term z_a * sum_w(q_w): every input channel of a tap sees the same sum of grad_out
+            gsum_b = gy.view(B, L, Cout).sum(dim=0)                                          # [L, Cout]
+            tap_grad = (_valid_taps(geom, gy.device) @ gsum_b).t().reshape(Cout, 1, kh, kw)
+            g_qw = gwmat.t().reshape(weight.shape) + z_a * tap_grad
+            q = torch.round(weight / s_w - z_w)
+            gw = torch.where((q >= 0) & (q <= w_qmax), s_a * g_qw, torch.zeros_like(g_qw))
+        if has_bias and ctx.needs_input_grad[2]:
+            gb = gy.sum(dim=0)
+        return gx, gw, gb, None, None, None, None, None, None
 
 
 class _MinMax(nn.Module):
@@ -102,6 +219,10 @@ class AppConv2d(nn.Conv2d, _AppQuant):
 
     def forward(self, x):
         self._refresh(x, self.weight)
+        if self.conv_impl == "layer" and not self.use_ste_gradient and x.is_cuda:
+            quant = torch.cat([self.activation_scale, self.activation_zp_neg, self.weight_scale, self.weight_zp_neg])
+            return _AppConvLayer.apply(x, self.weight, self.bias, quant, self.a_qmax, self.w_qmax, self.stride[0],
+                                       self.padding[0], self.dilation[0])
         xq = self._codes(x, self.activation_scale, self.activation_zp_neg, self.a_qmax)
         wq = self._codes(self.weight, self.weight_scale, self.weight_zp_neg, self.w_qmax)
         geo = dict(stride=self.stride, padding=self.padding, dilation=self.dilation)

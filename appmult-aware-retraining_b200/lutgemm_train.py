@@ -35,7 +35,7 @@ def install_tables(device, bits: int, lut_file: str | None) -> None:
         self_ops.set_lookup_tables(device, fp, ga, gb, bits)
 
 
-def build(device, bits: int, conv_impl: str = "fused", use_ste: bool = False, lr: float = 0.01, num_classes: int = 10):
+def build(device, bits: int, conv_impl: str = "layer", use_ste: bool = False, lr: float = 0.01, num_classes: int = 10):
     torch.manual_seed(0)  # identical initial weights on every rank
     model = resnet18_cifar(num_classes).to(device)
     prepare(model, a_bits=bits, w_bits=bits, use_ste_gradient=use_ste, conv_impl=conv_impl)
@@ -61,7 +61,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--lr", type=float, default=0.01)
     ap.add_argument("--ste", action="store_true", help="straight-through backward instead of the gradient tables")
-    ap.add_argument("--conv-impl", choices=["fused", "unfold"], default="fused")
+    ap.add_argument("--conv-impl", choices=["layer", "fused", "unfold"], default="layer")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     device = torch.device(f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}")

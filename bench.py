@@ -490,7 +490,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", choices=["lutgemm", "resnet18"], default="lutgemm")
     ap.add_argument("--batch", type=int, default=256, help="per-GPU batch of the resnet18 workload")
-    ap.add_argument("--conv-impl", choices=["fused", "unfold"], default="fused")
+    ap.add_argument("--conv-impl", choices=["layer", "fused", "unfold"], default="layer")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))

@@ -113,6 +113,44 @@ int lutgemm_conv2d_backward(const float *gy, const uint8_t *x, const uint8_t *wm
                             size_t scratch_bytes, void *stream);
 
 /*
+ * Quantisation prologue of an approximate convolution layer, one pass:
+ *   codes[b,c,h,w] = uint8(clamp(rint(x[b,c,h,w] / *scale - *zp_neg), 0, qmax))     NCHW-contiguous
+ *   chansum[b,h,w] += sum_c codes[b,c,h,w]      (optional; the caller zeroes it; exact, the sums are integers)
+ * x is any dense 4-D fp32 tensor given by its element strides (NCHW or channels-last); scale and zp_neg are
+ * device pointers to one float each (module buffers), so nothing synchronises with the host.
+ * Replaces the elementwise chain of ApproxConv2d.forward, micronet+/app_layers.py:147-150,163-166
+ * (x / scale - zero_point, round with straight-through gradient, clamp) and the uint8 cast of
+ * self_ops/ops_py/approx_ops.py:563.
+ */
+int lutgemm_quantize_activations(const float *x, long stride_b, long stride_c, long stride_h, long stride_w, int B,
+                                 int C, int H, int W, const float *scale, const float *zp_neg, float qmax,
+                                 uint8_t *codes, float *chansum, void *stream);
+
+/*
+ * Backward of the prologue (straight-through rounding, clamp mask), fused with the zero-point cross term
+ * and the weight scale:
+ *   gx[b,c,h,w] = [0 <= rint(x / *scale - *zp_neg) <= qmax] * *s_w * (gcodes[b,c,h,w] + *z_w * box_t[b,h,w])
+ * gcodes is NCHW-contiguous (what lutgemm_conv2d_backward returns for an un-scaled grad_out), box_t may be
+ * NULL, gx has the strides of x.  Replaces the autograd chain of the same lines.
+ */
+int lutgemm_quantize_activations_backward(const float *x, long stride_b, long stride_c, long stride_h, long stride_w,
+                                          int B, int C, int H, int W, const float *scale, const float *zp_neg,
+                                          float qmax, const float *gcodes, const float *box_t, const float *s_w,
+                                          const float *z_w, float *gx, void *stream);
+
+/*
+ * De-quantisation epilogue of an approximate convolution layer, one pass over the accumulators:
+ *   out[m,co] = *s_a * *s_w * (y[m,co] + *z_w * box[m] + *z_a * sumw_t[l,co] + *z_a * *z_w * taps[l]) (+ bias[co])
+ * with m = b*L + l, y the uint32 result of lutgemm_conv2d_forward ([M, Cout]), box [M] the window sums of the
+ * activation codes, sumw_t [L, Cout] the window sums of the weight codes, taps [L] the valid-tap counts times
+ * Cin; each product and sum is rounded separately, in this order.  bias may be NULL.
+ * Replaces micronet+/app_layers.py:175-184 (three cross-term convolutions, adds, scale).
+ */
+int lutgemm_conv2d_epilogue(const uint32_t *y, const float *box, const float *sumw_t, const float *taps,
+                            const float *s_a, const float *s_w, const float *z_a, const float *z_w, const float *bias,
+                            float *out, long M, int L, int Cout, void *stream);
+
+/*
  * Weight gradient only, with no device memory taken from anyone: same result as lutgemm_backward with
  * ga == NULL, but the kernels' partial sums go to a fixed array inside the library image instead of a
  * caller-supplied scratch buffer.  Meant for callers that may not allocate when the gradient is due -

@@ -7,6 +7,7 @@ and the max error relative to the largest gradient magnitude must not exceed 1e-
 import numpy as np
 import pytest
 import torch
+import torch.nn.functional as F
 
 from oracle import oracle_np as O
 
@@ -300,3 +301,58 @@ def test_bounded_wait_times_out_and_reports(dev):
     assert approx_ops.device_error() == 0  # reading clears it
     x = torch.ones(8, device=dev)
     assert float(x.sum()) == 8.0
+
+
+@pytest.mark.parametrize("bits", [7, 8])
+def test_whole_layer_kernels_match_the_autograd_expression(dev, bits, monkeypatch):
+    """AppConv2d with conv_impl="layer" (quantisation prologue, LUT convolution, de-quantisation epilogue and
+    their fused backward) against the same layer evaluated op by op by autograd (conv_impl="fused"): identical
+    activation codes, outputs and gradients to fp32 rounding."""
+    import self_ops
+    from lutgemm_layers import AppConv2d
+    fp, ga_t, gb_t = O.synthetic_tables(bits, seed=40 + bits)
+    self_ops.set_lookup_tables(dev, fp, ga_t, gb_t, bits)
+    # the op-by-op expression evaluates its cross terms with library convolutions: keep those in full fp32
+    monkeypatch.setattr(torch.backends.cudnn, "allow_tf32", False)
+    cases = [(4, 3, 12, 12, 8, 3, 1, 1, False, False), (2, 40, 9, 11, 33, 3, 2, 1, True, True),
+             (3, 64, 8, 8, 64, 1, 2, 0, False, True), (2, 16, 10, 10, 24, 3, 1, 2, True, False)]
+    for s_, (B, Cin, H, W, Cout, k, st, p, bias, cl) in enumerate(cases):
+        torch.manual_seed(100 * bits + s_)
+        ref = AppConv2d(Cin, Cout, k, st, p, 1, 1, bias, bits, bits, False, "fused").to(dev).train()
+        new = AppConv2d(Cin, Cout, k, st, p, 1, 1, bias, bits, bits, False, "layer").to(dev).train()
+        new.load_state_dict(ref.state_dict())
+        x = torch.randn(B, Cin, H, W, device=dev) * 1.5 + 0.3
+        if cl:
+            x = x.contiguous(memory_format=torch.channels_last)
+        xr, xn = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+        yr, yn = ref(xr), new(xn)
+        assert yr.shape == yn.shape
+        # The output is a small difference of large terms (LUT sum against zero-point cross terms), and the
+        # library convolutions of the op-by-op expression are not exact in fp32: allow a few fp32 roundings of
+        # the largest term.
+        qmax = float((1 << bits) - 1)
+        s_a, z_a, s_w, z_w = (float(t) for t in (new.activation_scale, new.activation_zp_neg, new.weight_scale,
+                                                  new.weight_zp_neg))
+        kdim = Cin * k * k
+        mag = s_a * s_w * kdim * (qmax * qmax + (abs(z_a) + abs(z_w)) * qmax + abs(z_a * z_w))
+        assert float((yr - yn).detach().abs().max()) <= 4 * 1.2e-7 * mag, (bits, s_)
+        g = torch.randn_like(yr)
+        yr.backward(g)
+        yn.backward(g)
+        # Each gradient is the sum of a LUT term and a zero-point cross term that largely cancel, and the two
+        # evaluations round them in different places: the tolerance is 1e-5 of the size of the terms, not of
+        # their (smaller) sum.
+        s_a, z_a, s_w, z_w = new.activation_scale, new.activation_zp_neg, new.weight_scale, new.weight_zp_neg
+        ones_k = torch.ones(1, 1, k, k, device=dev)
+        Ho, Wo = yr.shape[2], yr.shape[3]
+        opad = (H - ((Ho - 1) * st - 2 * p + (k - 1) + 1), W - ((Wo - 1) * st - 2 * p + (k - 1) + 1))
+        box_t = F.conv_transpose2d(g.sum(dim=1, keepdim=True), ones_k, stride=st, padding=p, output_padding=opad)
+        tap = torch.nn.grad.conv2d_weight(torch.ones(1, 1, H, W, device=dev), (Cout, 1, k, k), g.sum(dim=0, keepdim=True),
+                                          stride=st, padding=p)
+        cross = {"x": float((s_w * z_w * box_t).abs().max()), "w": float((s_a * z_a * tap).abs().max())}
+        for a_, b_, name in ((xr.grad, xn.grad, "x"), (ref.weight.grad, new.weight.grad, "w")):
+            scale_ = float(a_.abs().max()) + 2.0 * cross[name]
+            assert float((a_ - b_).abs().max()) <= 1e-5 * scale_ + 1e-30, (bits, s_, name)
+        if bias:
+            assert torch.allclose(ref.bias.grad, new.bias.grad, rtol=1e-5, atol=1e-6)
+        assert xn.grad.stride() == xn.stride()
