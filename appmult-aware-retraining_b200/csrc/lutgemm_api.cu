@@ -60,10 +60,11 @@ struct BackwardPlan {
 // LUTGEMM_BACKWARD_KERNEL=bcast|slab overrides (for A/B timing).
 BackwardPlan plan_backward(int bits, int M, int K, int N, int sms) {
     BackwardPlan pl{};
-    // measured on B200 at 4096^3 (ms, grad_w / grad_a): fp32-slab 19.8 / 20.7 (8 bit), 16.9 / 16.9 (7 bit),
-    // 15.3 / 15.3 (6 bit) against broadcast 24.5 / 23.9, 18.4 / 17.9, 12.0 / 13.0: the slab kernels win
-    // where the broadcast gathers suffer bank conflicts (7 and 8 bits); at 4 and 6 bits a table row is
-    // conflict-free already
+    // measured on B200 at 4096^3 (ms, grad_w / grad_a): tall fp32-slab 15.9 / 16.4 (8 bit), 14.1 / 14.4 (7 bit)
+    // against broadcast about 24 / 24 and 17 / 17: the slab kernels win where the broadcast gathers suffer
+    // bank conflicts (7 and 8 bits); at 4 and 6 bits a table row is conflict-free and the broadcast kernels
+    // (11.5 / 11.6) beat the slab kernels.  grad_a needs N >= 768 for a slab: on convolution shapes with
+    // N <= 512 the column-broadcast kernel is faster at both 7 and 8 bits.
     pl.gw_slab = bits >= 7 && M >= 512 && N >= 32 && slab_fill(M, N) >= 0.6;
     pl.ga_slab = bits >= 7 && N >= 768 && M >= 32 && slab_fill(N, M) >= 0.6;
     if (env_is("LUTGEMM_BACKWARD_KERNEL", "bcast")) pl.gw_slab = pl.ga_slab = false;

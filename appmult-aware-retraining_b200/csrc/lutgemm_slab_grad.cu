@@ -313,11 +313,11 @@ __global__ void __launch_bounds__(32 * WARPS, 1) slab_grad_kernel(const Args p) 
                 const uint32_t ub = u_addr + (NBUF == 2 ? (k & 1) : 0) * C::U_BYTES + lane * 8;
                 float s0a = 0.f, s0b = 0.f, s1a = 0.f, s1b = 0.f;
                 float pf0[PF], pf1[PF];
-#define ROW_ADDR(v, i) (ub + byte_of(v, i) * (US * 4))
+                auto row_addr = [&](uint32_t v, int i) { return ub + byte_of(v, i) * (US * 4); };
 #pragma unroll
                 for (int r = 0; r < PF; ++r) {
                     asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];"
-                                 : "=f"(pf0[r]), "=f"(pf1[r]) : "r"(ROW_ADDR(rv[r >> 2], r & 3)));
+                                 : "=f"(pf0[r]), "=f"(pf1[r]) : "r"(row_addr(rv[r >> 2], r & 3)));
                 }
 #pragma unroll
                 for (int r = 0; r < RW; ++r) {
@@ -325,7 +325,7 @@ __global__ void __launch_bounds__(32 * WARPS, 1) slab_grad_kernel(const Args p) 
                     if (r + PF < RW) {
                         asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];"
                                      : "=f"(pf0[r % PF]), "=f"(pf1[r % PF])
-                                     : "r"(ROW_ADDR(rv[(r + PF) >> 2], (r + PF) & 3)));
+                                     : "r"(row_addr(rv[(r + PF) >> 2], (r + PF) & 3)));
                     }
                     if (r & 1) { s0b = fmaf(f0, g[r][0], s0b); s1b = fmaf(f1, g[r][1], s1b); }
                     else       { s0a = fmaf(f0, g[r][0], s0a); s1a = fmaf(f1, g[r][1], s1a); }

@@ -18,12 +18,6 @@
 #include "lutgemm_common.cuh"
 #include "lutgemm_kernels.h"
 
-#ifndef LUTGEMM_TALL_VAR
-#define LUTGEMM_TALL_VAR 0
-#endif
-#ifndef LUTGEMM_TALL_PF
-#define LUTGEMM_TALL_PF 4
-#endif
 
 namespace lutgemm {
 namespace sgt {
@@ -318,55 +312,25 @@ __global__ void __launch_bounds__(512, 1) slab_grad_tall_kernel(const Args p) {
                 const uint32_t ub = u_addr + (k & 1) * C::U_BYTES + lane * 4;
                 float s[4] = {0.f, 0.f, 0.f, 0.f};
                 // slab row address = base + 136 * code in one integer dot-product instruction
-#define ROW_ADDR(v, i) byte_scaled_add<US * 4>(v, i, ub)
-#if (LUTGEMM_TALL_VAR & 2)
-                // batches of PF rows: all loads of a batch, then its FMAs
-#pragma unroll
-                for (int r0_ = 0; r0_ < RW; r0_ += 16) {
-                    const uint4 t = rp[r0_ / 16];
-                    const uint32_t rv[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-                    for (int rb = 0; rb < 16; rb += PF) {
-                        float f[PF];
-#pragma unroll
-                        for (int j = 0; j < PF; ++j)
-                            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(f[j]) : "r"(ROW_ADDR(rv[(rb + j) >> 2], (rb + j) & 3)));
-#pragma unroll
-                        for (int j = 0; j < PF; ++j) s[j & 3] = fmaf(f[j], g[r0_ + rb + j], s[j & 3]);
-                    }
-                }
-#else
+                auto row_addr = [&](uint32_t v, int i) { return byte_scaled_add<US * 4>(v, i, ub); };
                 uint32_t rv[RW / 4];
-#if (LUTGEMM_TALL_VAR & 1)
-                { const uint4 t = rp[0]; rv[0] = t.x; rv[1] = t.y; rv[2] = t.z; rv[3] = t.w; }
-#else
 #pragma unroll
                 for (int q = 0; q < RW / 16; ++q) {
                     const uint4 t = rp[q];
                     rv[4 * q] = t.x; rv[4 * q + 1] = t.y; rv[4 * q + 2] = t.z; rv[4 * q + 3] = t.w;
                 }
-#endif
                 float pf[PF];
 #pragma unroll
                 for (int r = 0; r < PF; ++r)
-                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(pf[r]) : "r"(ROW_ADDR(rv[r >> 2], r & 3)));
+                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(pf[r]) : "r"(row_addr(rv[r >> 2], r & 3)));
 #pragma unroll
                 for (int r = 0; r < RW; ++r) {
                     const float f = pf[r % PF];
-#if (LUTGEMM_TALL_VAR & 1)
-                    // the codes of rows 16q .. 16q+15 are fetched eight rows before their first use
-                    if ((r + PF + 8) % 16 == 0 && r + PF + 8 < RW) {
-                        const int q = (r + PF + 8) / 16;
-                        const uint4 t = rp[q];
-                        rv[4 * q] = t.x; rv[4 * q + 1] = t.y; rv[4 * q + 2] = t.z; rv[4 * q + 3] = t.w;
-                    }
-#endif
                     if (r + PF < RW)
                         asm volatile("ld.shared.f32 %0, [%1];"
-                                     : "=f"(pf[r % PF]) : "r"(ROW_ADDR(rv[(r + PF) >> 2], (r + PF) & 3)));
+                                     : "=f"(pf[r % PF]) : "r"(row_addr(rv[(r + PF) >> 2], (r + PF) & 3)));
                     s[r & 3] = fmaf(f, g[r], s[r & 3]);
                 }
-#endif
                 part_s[(k & 1) * (WARPS * PS) + wp * PS + lane] = (s[0] + s[1]) + (s[2] + s[3]);
             };
             if (side_first) { side_work(); use_phase(); } else { use_phase(); side_work(); }
@@ -388,7 +352,7 @@ static int launch_slab_grad_tall(const float *gc, const uint8_t *a, const uint8_
     using C = sgt::Cfg<BITS>;
     static_assert(C::RT == kSlabTallRows, "tile height");
     static_assert(C::SMEM <= 232448, "shared memory budget");
-    auto kern = sgt::slab_grad_tall_kernel<BITS, MODE, LUTGEMM_TALL_PF>;
+    auto kern = sgt::slab_grad_tall_kernel<BITS, MODE, 4>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
         return LUTGEMM_E_CUDA;
     const int RDIM = MODE == sgt::kGa ? N : M, CDIM = MODE == sgt::kGa ? M : N;
