@@ -158,8 +158,9 @@ int lutgemm_conv2d_epilogue(const uint32_t *y, const float *box, const float *su
  * allocator, code on a path where cudaMalloc's implicit synchronisation is not acceptable.
  *   - The array is LUTGEMM_NOALLOC_SCRATCH_BYTES (32 MiB) per GPU that loads the library, held until
  *     the process exits; lutgemm_noalloc_scratch_capacity() returns the figure.  A problem whose partial
- *     sums need more is refused with LUTGEMM_E_TOOLARGE (they need ceil(M/512)*K*N*4 bytes on the slab
- *     path, splits*K*N*4 on the split-M path, nothing for small M).
+ *     sums need more is refused with LUTGEMM_E_TOOLARGE (lutgemm_backward_scratch_bytes tells the need: on
+ *     the slab path one K*N*4-byte block per 1024 or 512 rows of M plus a transposed copy of the codes,
+ *     K*M bytes; splits*K*N*4 on the split-M path; nothing for small M).
  *   - The first call made with a given device current looks up the array's address on that device
  *     (cudaGetSymbolAddress); make that first call before any stream capture begins.
  *   - All calls share the one array per device and it keeps whatever the last call left there.  Nothing
