@@ -535,7 +535,53 @@ __global__ void __launch_bounds__(1024) transpose_codes_kernel(const uint8_t *__
     *reinterpret_cast<uint4 *>(at + (size_t)k * pitch + m0) = make_uint4(v[0], v[1], v[2], v[3]);
 }
 
+// The same for a convolution whose output plane is a multiple of 16 positions and whose input plane fits
+// shared memory: one CTA stages the plane x[b,c,:,:] once (coalesced) and writes the kh*kw shifted copies of
+// it, 16 output positions per thread and store.
+__global__ void __launch_bounds__(256) transpose_codes_plane_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ at,
+                                                                    int pitch, const ConvGeom g) {
+    extern __shared__ __align__(16) uint8_t plane[];
+    const int bc = blockIdx.x, b = bc / g.C, c = bc - b * g.C;
+    const int HW = g.H * g.W, L = g.Ho * g.Wo, kk = g.kh * g.kw;
+    const uint8_t *src = x + (size_t)bc * HW;
+    if ((HW & 15) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+        for (int i = threadIdx.x; i < HW / 16; i += blockDim.x)
+            reinterpret_cast<uint4 *>(plane)[i] = reinterpret_cast<const uint4 *>(src)[i];
+    } else {
+        for (int i = threadIdx.x; i < HW; i += blockDim.x) plane[i] = src[i];
+    }
+    __syncthreads();
+    const int chunks = L / 16;
+    for (int q = threadIdx.x; q < kk * chunks; q += blockDim.x) {
+        const int tap = q / chunks, l0 = (q - tap * chunks) * 16;
+        const int i = tap / g.kw, j = tap - i * g.kw;
+        const int dh = i * g.dil - g.pad, dw = j * g.dil - g.pad;
+        int oh = l0 / g.Wo, ow = l0 - oh * g.Wo;
+        uint32_t v[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            const int ih = oh * g.stride + dh, iw = ow * g.stride + dw;
+            if ((unsigned)ih < (unsigned)g.H && (unsigned)iw < (unsigned)g.W)
+                v[e >> 2] |= (uint32_t)plane[ih * g.W + iw] << (8 * (e & 3));
+            if (++ow == g.Wo) { ow = 0; ++oh; }
+        }
+        *reinterpret_cast<uint4 *>(at + (size_t)(c * kk + tap) * pitch + (size_t)b * L + l0) =
+            make_uint4(v[0], v[1], v[2], v[3]);
+    }
+}
+
 int transpose_codes(const uint8_t *a, uint8_t *at, int M, int K, int pitch, const ConvGeom &conv, cudaStream_t stream) {
+    // (small planes leave a CTA too little to do: they take the generic kernel)
+    if (conv.enabled && (conv.Ho * conv.Wo) % 16 == 0 && conv.Ho * conv.Wo >= 256 && conv.H * conv.W <= 96 * 1024 &&
+        (long)conv.B * conv.C <= 0x7fffffffL) {
+        // every column m < M is written (M = B * Ho * Wo is a multiple of 16, so pitch == M)
+        const int smem = (conv.H * conv.W + 15) & ~15;
+        if (smem > 48 * 1024 &&
+            cudaFuncSetAttribute(transpose_codes_plane_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return LUTGEMM_E_CUDA;
+        transpose_codes_plane_kernel<<<conv.B * conv.C, 256, smem, stream>>>(a, at, pitch, conv);
+        return cudaGetLastError() == cudaSuccess ? LUTGEMM_OK : LUTGEMM_E_CUDA;
+    }
     const dim3 block(32, 32), grid((pitch / 16 + 31) / 32, (K + 31) / 32);
     if (grid.y > 65535u) return LUTGEMM_E_TOOLARGE;
     transpose_codes_kernel<<<grid, block, 0, stream>>>(a, at, M, K, pitch, conv);
