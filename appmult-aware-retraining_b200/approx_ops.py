@@ -46,6 +46,16 @@ def _load():
     lib.lutgemm_bits_from_elem_num.argtypes = [cl]
     lib.lutgemm_forward.restype = ci
     lib.lutgemm_forward.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, vp]
+    lib.lutgemm_forward_scratch_bytes.restype = sz
+    lib.lutgemm_forward_scratch_bytes.argtypes = [ci, ci, ci, ci]
+    lib.lutgemm_forward_ws.restype = ci
+    lib.lutgemm_forward_ws.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, vp, sz, vp]
+    lib.lutgemm_conv2d_forward_scratch_bytes.restype = sz
+    lib.lutgemm_conv2d_forward_scratch_bytes.argtypes = [ci] * 11
+    lib.lutgemm_conv2d_forward_ws.restype = ci
+    lib.lutgemm_conv2d_forward_ws.argtypes = [vp, vp, vp, vp] + [ci] * 11 + [vp, sz, vp]
+    lib.lutgemm_conv2d_backward_ws.restype = ci
+    lib.lutgemm_conv2d_backward_ws.argtypes = [vp] * 7 + [ci] * 11 + [vp, vp, sz, vp]
     lib.lutgemm_backward_scratch_bytes.restype = sz
     lib.lutgemm_backward_scratch_bytes.argtypes = [ci, ci, ci, ci]
     lib.lutgemm_backward.restype = ci
@@ -136,9 +146,13 @@ def approx_gemm_forward(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, lut: 
     if K == 0:
         c.zero_()
         return
+    lib = _load()
     with torch.cuda.device(dev):
-        rc = _load().lutgemm_forward(a.data_ptr(), b.data_ptr(), c.data_ptr(), lut.data_ptr(), bits, M, K, N,
-                                     _stream_ptr(dev))
+        # workspace for the transposed activation codes (0 bytes when the kernel for this shape has no use for it)
+        nbytes = lib.lutgemm_forward_scratch_bytes(bits, M, K, N)
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev) if nbytes else None
+        rc = lib.lutgemm_forward_ws(a.data_ptr(), b.data_ptr(), c.data_ptr(), lut.data_ptr(), bits, M, K, N,
+                                    scratch.data_ptr() if nbytes else None, nbytes, _stream_ptr(dev))
     _check(rc, "approx_gemm_forward")
 
 
@@ -204,10 +218,12 @@ def _conv_out(H, W, kh, kw, stride, pad, dil):
 
 
 def approx_conv2d_forward(x: torch.Tensor, wmat: torch.Tensor, y: torch.Tensor, lut: torch.Tensor, kh: int, kw: int,
-                          stride: int, pad: int, dil: int) -> None:
+                          stride: int, pad: int, dil: int):
     """Fused-im2col convolution forward.  x: u8 codes [B,C,H,W]; wmat: u8 [C*kh*kw, Cout]; y: u32
     [B*Ho*Wo, Cout] (NHWC), written in place.  The reference declares such an op
-    (`approx_conv2d_forward`, self_ops/src/op_register.cpp:11,22) but ships no source for it."""
+    (`approx_conv2d_forward`, self_ops/src/op_register.cpp:11,22) but ships no source for it.
+    Returns the transposed unfolded codes the kernel worked from (a uint8 tensor to hand to
+    `approx_conv2d_backward(..., codes_t=...)` of the same layer), or None when the shape did not need them."""
     _check_input(x, torch.uint8, "input_tensor")
     _check_input(wmat, torch.uint8, "weight_tensor")
     _check_input(y, torch.uint32, "output_tensor")
@@ -224,17 +240,23 @@ def approx_conv2d_forward(x: torch.Tensor, wmat: torch.Tensor, y: torch.Tensor, 
     bits = _bits_of(lut, "lut_appmult_tensor")
     if wmat.device != x.device or y.device != x.device or lut.device != x.device:
         raise RuntimeError("device id not match")
+    lib = _load()
     with torch.cuda.device(x.device):
-        rc = _load().lutgemm_conv2d_forward(x.data_ptr(), wmat.data_ptr(), y.data_ptr(), lut.data_ptr(), bits, B, C, H,
-                                            W, Cout, kh, kw, stride, pad, dil, _stream_ptr(x.device))
+        nbytes = lib.lutgemm_conv2d_forward_scratch_bytes(bits, B, C, H, W, Cout, kh, kw, stride, pad, dil)
+        codes_t = torch.empty(nbytes, dtype=torch.uint8, device=x.device) if nbytes else None
+        rc = lib.lutgemm_conv2d_forward_ws(x.data_ptr(), wmat.data_ptr(), y.data_ptr(), lut.data_ptr(), bits, B, C, H,
+                                           W, Cout, kh, kw, stride, pad, dil, codes_t.data_ptr() if nbytes else None,
+                                           nbytes, _stream_ptr(x.device))
     _check(rc, "approx_conv2d_forward")
+    return codes_t
 
 
 def approx_conv2d_backward(gy: torch.Tensor, x: torch.Tensor, wmat: torch.Tensor, gx: torch.Tensor, gw: torch.Tensor,
                            lut_grad_a: torch.Tensor, lut_grad_b: torch.Tensor, kh: int, kw: int, stride: int, pad: int,
-                           dil: int) -> None:
+                           dil: int, codes_t: torch.Tensor = None) -> None:
     """Fused-im2col convolution backward.  gy: f32 [B*Ho*Wo, Cout]; gx: f32 [B,C,H,W] and gw: f32
-    [C*kh*kw, Cout] are written in place; either may be None to skip that gradient."""
+    [C*kh*kw, Cout] are written in place; either may be None to skip that gradient.  codes_t: what
+    `approx_conv2d_forward` returned for the same x and geometry (optional)."""
     _check_input(gy, torch.float32, "grad_output_tensor")
     _check_input(x, torch.uint8, "input_tensor")
     _check_input(wmat, torch.uint8, "weight_tensor")
@@ -262,11 +284,16 @@ def approx_conv2d_backward(gy: torch.Tensor, x: torch.Tensor, wmat: torch.Tensor
     with torch.cuda.device(dev):
         nbytes = lib.lutgemm_conv2d_backward_scratch_bytes(bits, B, C, H, W, Cout, kh, kw, stride, pad, dil)
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
-        rc = lib.lutgemm_conv2d_backward(gy.data_ptr(), x.data_ptr(), wmat.data_ptr(),
-                                         gx.data_ptr() if gx is not None else None,
-                                         gw.data_ptr() if gw is not None else None,
-                                         lut_grad_a.data_ptr(), lut_grad_b.data_ptr(), bits, B, C, H, W, Cout, kh, kw,
-                                         stride, pad, dil, scratch.data_ptr(), nbytes, _stream_ptr(dev))
+        if codes_t is not None:
+            _check_input(codes_t, torch.uint8, "codes_t")
+            if codes_t.numel() != K * ((B * Ho * Wo + 15) // 16 * 16):
+                raise RuntimeError("codes_t does not belong to this convolution")
+        rc = lib.lutgemm_conv2d_backward_ws(gy.data_ptr(), x.data_ptr(), wmat.data_ptr(),
+                                            gx.data_ptr() if gx is not None else None,
+                                            gw.data_ptr() if gw is not None else None,
+                                            lut_grad_a.data_ptr(), lut_grad_b.data_ptr(), bits, B, C, H, W, Cout, kh, kw,
+                                            stride, pad, dil, codes_t.data_ptr() if codes_t is not None else None,
+                                            scratch.data_ptr(), nbytes, _stream_ptr(dev))
     _check(rc, "approx_conv2d_backward")
 
 

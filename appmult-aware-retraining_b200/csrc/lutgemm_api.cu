@@ -125,26 +125,44 @@ int lutgemm_bits_from_elem_num(long elem_num) {
 }
 
 // ---- shared bodies of the GEMM and the implicit-im2col entry points ------------------------------------
-static int forward_impl(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K,
-                        int N, const lutgemm::ConvGeom &conv, void *stream) {
-    if (!lutgemm::bits_supported(bits)) return LUTGEMM_E_BITS;
-    if (!a || !w || !c || !lut || M <= 0 || K <= 0 || N <= 0) return LUTGEMM_E_BADARG;
-    if ((reinterpret_cast<uintptr_t>(c) & 3) || (reinterpret_cast<uintptr_t>(lut) & 1)) return LUTGEMM_E_BADARG;
-    const int sms = current_num_sms();
-    if (sms <= 0) return LUTGEMM_E_CUDA;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // Large-M problems with reasonably filled 512x64 tiles go to the slab kernel; small or skinny ones
-    // to the row-broadcast kernel.  LUTGEMM_FORWARD_KERNEL=rowbcast|slab overrides (for A/B timing).
+// Large-M problems with reasonably filled 512x64 tiles go to the slab kernel; small or skinny ones to the
+// row-broadcast kernel.  LUTGEMM_FORWARD_KERNEL=rowbcast|slab overrides (for A/B timing).
+static bool forward_uses_slab(int M, int N) {
     bool slab = M >= 512 && N >= 32 && slab_fill(M, N) >= 0.6;
     if (env_is("LUTGEMM_FORWARD_KERNEL", "rowbcast")) slab = false;
     if (env_is("LUTGEMM_FORWARD_KERNEL", "slab")) slab = true;
-    if (slab) {
+    return slab;
+}
+
+static int codes_pitch(int M) { return (M + 15) & ~15; }
+
+// `scratch` (optional, K * codes_pitch(M) bytes, 16-byte aligned): the slab kernel then reads the activation
+// codes from a transposed copy made there first, which stays valid on return.
+static int forward_impl(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K,
+                        int N, const lutgemm::ConvGeom &conv, void *scratch, size_t scratch_bytes, void *stream) {
+    if (!lutgemm::bits_supported(bits)) return LUTGEMM_E_BITS;
+    if (!a || !w || !c || !lut || M <= 0 || K <= 0 || N <= 0) return LUTGEMM_E_BADARG;
+    if ((reinterpret_cast<uintptr_t>(c) & 3) || (reinterpret_cast<uintptr_t>(lut) & 1) ||
+        (reinterpret_cast<uintptr_t>(scratch) & 15))
+        return LUTGEMM_E_BADARG;
+    const int sms = current_num_sms();
+    if (sms <= 0) return LUTGEMM_E_CUDA;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (forward_uses_slab(M, N)) {
         // Two implementations of the slab algorithm: barrier-synchronous (default: faster on B200 at 7 and
-        // 8 bits, 12.8 vs 17.6 ms at 8-bit 4096^3, where four producer warps cannot build slabs fast
-        // enough) and warp-specialised (LUTGEMM_SLAB_IMPL=ws, plain GEMM operands only).
+        // 8 bits, where four producer warps cannot build slabs fast enough) and warp-specialised
+        // (LUTGEMM_SLAB_IMPL=ws, plain GEMM operands only).
         if (!conv.enabled && env_is("LUTGEMM_SLAB_IMPL", "ws"))
             return lutgemm::forward_slab_ws(a, w, c, lut, bits, M, K, N, sms, s);
-        return lutgemm::forward_slab(a, w, c, lut, bits, M, K, N, conv, sms, s);
+        const uint8_t *at = nullptr;
+        const int pitch = codes_pitch(M);
+        if (scratch) {
+            if (scratch_bytes < (size_t)pitch * K) return LUTGEMM_E_SCRATCH;
+            const int trc = lutgemm::transpose_codes(a, static_cast<uint8_t *>(scratch), M, K, pitch, conv, s);
+            if (trc != LUTGEMM_OK) return trc;
+            at = static_cast<const uint8_t *>(scratch);
+        }
+        return lutgemm::forward_slab(a, w, c, lut, bits, M, K, N, conv, at, pitch, sms, s);
     }
     return lutgemm::forward_rowbcast(a, w, c, lut, bits, M, K, N, conv, sms, s);
 }
@@ -152,7 +170,19 @@ static int forward_impl(const uint8_t *a, const uint8_t *w, uint32_t *c, const u
 int lutgemm_forward(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K,
                     int N, void *stream) {
     lutgemm::ConvGeom none{};
-    return forward_impl(a, w, c, lut, bits, M, K, N, none, stream);
+    return forward_impl(a, w, c, lut, bits, M, K, N, none, nullptr, 0, stream);
+}
+
+size_t lutgemm_forward_scratch_bytes(int bits, int M, int K, int N) {
+    if (!lutgemm::bits_supported(bits) || M <= 0 || K <= 0 || N <= 0) return 0;
+    if (!forward_uses_slab(M, N) || env_is("LUTGEMM_SLAB_IMPL", "ws")) return 0;
+    return (size_t)codes_pitch(M) * K;
+}
+
+int lutgemm_forward_ws(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K,
+                       int N, void *scratch, size_t scratch_bytes, void *stream) {
+    lutgemm::ConvGeom none{};
+    return forward_impl(a, w, c, lut, bits, M, K, N, none, scratch, scratch_bytes, stream);
 }
 
 int lutgemm_device_error(int *value) {
@@ -174,7 +204,8 @@ size_t lutgemm_backward_scratch_bytes(int bits, int M, int K, int N) {
 
 static int backward_impl(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, float *gw,
                          const int16_t *lut_ga, const int16_t *lut_gw, int bits, int M, int K, int N,
-                         const lutgemm::ConvGeom &conv, void *scratch, size_t scratch_bytes, void *stream) {
+                         const lutgemm::ConvGeom &conv, const uint8_t *codes_t, void *scratch, size_t scratch_bytes,
+                         void *stream) {
     if (!lutgemm::bits_supported(bits)) return LUTGEMM_E_BITS;
     if (!gc || !a || !w || M <= 0 || K <= 0 || N <= 0) return LUTGEMM_E_BADARG;
     if ((ga && !lut_ga) || (gw && !lut_gw)) return LUTGEMM_E_BADARG;
@@ -191,8 +222,8 @@ static int backward_impl(const float *gc, const uint8_t *a, const uint8_t *w, fl
     if (gw) {
         // the weight gradient goes first: under data parallelism its all-reduce can then overlap gA
         if (pl.gw_scratch && (!scratch || scratch_bytes < pl.gw_scratch)) return LUTGEMM_E_SCRATCH;
-        const uint8_t *at = nullptr;
-        if (pl.gw_slab && pl.gw_at_pitch && !ws_impl) {
+        const uint8_t *at = codes_t;  // left by the forward pass (same layout), or made here
+        if (pl.gw_slab && pl.gw_at_pitch && !ws_impl && !at) {
             uint8_t *dst = static_cast<uint8_t *>(scratch) + pl.gw_at_offset;
             const int trc = lutgemm::transpose_codes(a, dst, M, K, pl.gw_at_pitch, conv, s);
             if (trc != LUTGEMM_OK) return trc;
@@ -219,7 +250,7 @@ int lutgemm_backward(const float *gc, const uint8_t *a, const uint8_t *w, float 
                      const int16_t *lut_ga, const int16_t *lut_gw, int bits, int M, int K, int N, void *scratch,
                      size_t scratch_bytes, void *stream) {
     lutgemm::ConvGeom none{};
-    return backward_impl(gc, a, w, ga, gw, lut_ga, lut_gw, bits, M, K, N, none, scratch, scratch_bytes, stream);
+    return backward_impl(gc, a, w, ga, gw, lut_ga, lut_gw, bits, M, K, N, none, nullptr, scratch, scratch_bytes, stream);
 }
 
 // ---- convolution entry points (implicit im2col) ------------------------------------------------------------
@@ -241,7 +272,23 @@ int lutgemm_conv2d_forward(const uint8_t *x, const uint8_t *wmat, uint32_t *y, c
     lutgemm::ConvGeom g{};
     const int rc = make_geom(B, C, H, W, kh, kw, stride, pad, dil, &g);
     if (rc != LUTGEMM_OK) return rc;
-    return forward_impl(x, wmat, y, lut, bits, B * g.Ho * g.Wo, C * kh * kw, Cout, g, stream);
+    return forward_impl(x, wmat, y, lut, bits, B * g.Ho * g.Wo, C * kh * kw, Cout, g, nullptr, 0, stream);
+}
+
+size_t lutgemm_conv2d_forward_scratch_bytes(int bits, int B, int C, int H, int W, int Cout, int kh, int kw,
+                                            int stride, int pad, int dil) {
+    lutgemm::ConvGeom g{};
+    if (make_geom(B, C, H, W, kh, kw, stride, pad, dil, &g) != LUTGEMM_OK) return 0;
+    return lutgemm_forward_scratch_bytes(bits, B * g.Ho * g.Wo, C * kh * kw, Cout);
+}
+
+int lutgemm_conv2d_forward_ws(const uint8_t *x, const uint8_t *wmat, uint32_t *y, const uint16_t *lut, int bits, int B,
+                              int C, int H, int W, int Cout, int kh, int kw, int stride, int pad, int dil,
+                              void *scratch, size_t scratch_bytes, void *stream) {
+    lutgemm::ConvGeom g{};
+    const int rc = make_geom(B, C, H, W, kh, kw, stride, pad, dil, &g);
+    if (rc != LUTGEMM_OK) return rc;
+    return forward_impl(x, wmat, y, lut, bits, B * g.Ho * g.Wo, C * kh * kw, Cout, g, scratch, scratch_bytes, stream);
 }
 
 size_t lutgemm_conv2d_backward_scratch_bytes(int bits, int B, int C, int H, int W, int Cout, int kh, int kw,
@@ -253,23 +300,33 @@ size_t lutgemm_conv2d_backward_scratch_bytes(int bits, int B, int C, int H, int 
     return ((M * K * sizeof(float) + 15) & ~(size_t)15) + lutgemm_backward_scratch_bytes(bits, (int)M, (int)K, Cout);
 }
 
-int lutgemm_conv2d_backward(const float *gy, const uint8_t *x, const uint8_t *wmat, float *gx, float *gw,
-                            const int16_t *lut_ga, const int16_t *lut_gw, int bits, int B, int C, int H, int W,
-                            int Cout, int kh, int kw, int stride, int pad, int dil, void *scratch,
-                            size_t scratch_bytes, void *stream) {
+int lutgemm_conv2d_backward_ws(const float *gy, const uint8_t *x, const uint8_t *wmat, float *gx, float *gw,
+                               const int16_t *lut_ga, const int16_t *lut_gw, int bits, int B, int C, int H, int W,
+                               int Cout, int kh, int kw, int stride, int pad, int dil, const uint8_t *codes_t,
+                               void *scratch, size_t scratch_bytes, void *stream) {
     lutgemm::ConvGeom g{};
     int rc = make_geom(B, C, H, W, kh, kw, stride, pad, dil, &g);
     if (rc != LUTGEMM_OK) return rc;
+    if (reinterpret_cast<uintptr_t>(codes_t) & 15) return LUTGEMM_E_BADARG;
     const int M = B * g.Ho * g.Wo, K = C * kh * kw;
     const size_t col_bytes = gx ? (((size_t)M * K * sizeof(float) + 15) & ~(size_t)15) : 0;
     if (gx && (!scratch || scratch_bytes < col_bytes)) return LUTGEMM_E_SCRATCH;
     float *gcol = static_cast<float *>(scratch);
     void *rest = scratch ? static_cast<char *>(scratch) + col_bytes : nullptr;
     const size_t rest_bytes = scratch_bytes > col_bytes ? scratch_bytes - col_bytes : 0;
-    rc = backward_impl(gy, x, wmat, gx ? gcol : nullptr, gw, lut_ga, lut_gw, bits, M, K, Cout, g, rest, rest_bytes, stream);
+    rc = backward_impl(gy, x, wmat, gx ? gcol : nullptr, gw, lut_ga, lut_gw, bits, M, K, Cout, g, codes_t, rest,
+                       rest_bytes, stream);
     if (rc != LUTGEMM_OK) return rc;
     if (gx) return lutgemm::col2im_gather(gcol, gx, g, static_cast<cudaStream_t>(stream));
     return LUTGEMM_OK;
+}
+
+int lutgemm_conv2d_backward(const float *gy, const uint8_t *x, const uint8_t *wmat, float *gx, float *gw,
+                            const int16_t *lut_ga, const int16_t *lut_gw, int bits, int B, int C, int H, int W,
+                            int Cout, int kh, int kw, int stride, int pad, int dil, void *scratch,
+                            size_t scratch_bytes, void *stream) {
+    return lutgemm_conv2d_backward_ws(gy, x, wmat, gx, gw, lut_ga, lut_gw, bits, B, C, H, W, Cout, kh, kw, stride, pad,
+                                      dil, nullptr, scratch, scratch_bytes, stream);
 }
 
 // ---- layer prologue / epilogue ---------------------------------------------------------------------------

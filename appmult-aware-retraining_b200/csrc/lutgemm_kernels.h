@@ -12,8 +12,9 @@ struct ConvGeom;  // lutgemm_common.cuh; geometry.enabled == 0 means `a` is a pl
 int forward_rowbcast(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K,
                      int N, const ConvGeom &conv, int num_sms, cudaStream_t stream);
 
+// `at` (optional): the activation codes transposed, at[k][m] with rows at_pitch bytes apart (transpose_codes)
 int forward_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K, int N,
-                 const ConvGeom &conv, int num_sms, cudaStream_t stream);
+                 const ConvGeom &conv, const uint8_t *at, int at_pitch, int num_sms, cudaStream_t stream);
 
 // rows of the reduction dimension per CTA tile of the fp32-slab gradient kernels, and the block count
 constexpr int kSlabF32Rows = 512;

@@ -55,6 +55,8 @@ struct Args {
     int tiles_r, tiles_c, ksplits, k_per_split;
     int vec_a, vec_w, vec_c;
     ConvGeom conv;
+    const uint8_t *at;  // optional: the activation codes transposed, at[k][m], rows at_pitch bytes apart
+    int at_pitch;       // a multiple of 16; columns m >= M hold 0
 };
 
 template <int BITS>
@@ -94,7 +96,12 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p) {
     auto fetch_chunk = [&](int m0, int n0, int chunk) {
         const int kbase = chunk * KC;
         const int m = min(m0 + tid, M - 1);
-        if (kbase >= K) prc = make_uint4(0, 0, 0, 0);
+        if (p.at) {
+            // 16 rows of one k per thread, coalesced (instead of 16 k of one row, gathered for a convolution)
+            const int gk = kbase + tid / (RT / 16), gm = m0 + (tid % (RT / 16)) * 16;
+            prc = (gk < K && gm < p.at_pitch) ? *reinterpret_cast<const uint4 *>(p.at + (size_t)gk * p.at_pitch + gm)
+                                              : make_uint4(0, 0, 0, 0);
+        } else if (kbase >= K) prc = make_uint4(0, 0, 0, 0);
         else if (p.conv.enabled) prc = conv_code16(p.a, p.conv, m, kbase, K);
         else if (p.vec_a) prc = *reinterpret_cast<const uint4 *>(p.a + (size_t)m * K + kbase);
         else prc = load16(p.a + (size_t)m * K + kbase, min(16, K - kbase));
@@ -109,8 +116,13 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p) {
         // codes are masked to BITS bits here, once, so no stray code can index outside a slab or the table
         const uint32_t tr[4] = {prc.x & MASK4, prc.y & MASK4, prc.z & MASK4, prc.w & MASK4};
         uint8_t *rs = rc_s + stage * C::RC_STAGE;
+        if (p.at) {
+            *reinterpret_cast<uint4 *>(rs + (tid / (RT / 16)) * RT + (tid % (RT / 16)) * 16) =
+                make_uint4(tr[0], tr[1], tr[2], tr[3]);
+        } else {
 #pragma unroll
-        for (int q = 0; q < 16; ++q) rs[q * RT + tid] = (uint8_t)(tr[q >> 2] >> (8 * (q & 3)));
+            for (int q = 0; q < 16; ++q) rs[q * RT + tid] = (uint8_t)(tr[q >> 2] >> (8 * (q & 3)));
+        }
         if (tid < KC * CT / 16)
             *reinterpret_cast<uint4 *>(cc_s + stage * C::CC_STAGE + (tid / (CT / 16)) * CT + (tid % (CT / 16)) * 16) =
                 make_uint4(pcc.x & MASK4, pcc.y & MASK4, pcc.z & MASK4, pcc.w & MASK4);
@@ -204,7 +216,7 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p) {
 
 template <int BITS>
 static int launch_fwd_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int M, int K, int N,
-                           const ConvGeom &conv, int num_sms, cudaStream_t stream) {
+                           const ConvGeom &conv, const uint8_t *at, int at_pitch, int num_sms, cudaStream_t stream) {
     using C = sf::Cfg<BITS>;
     auto kern = sf::slab_fwd_kernel<BITS>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
@@ -212,6 +224,8 @@ static int launch_fwd_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, cons
     sf::Args p{};
     p.a = a; p.w = w; p.lut = lut; p.c = c; p.M = M; p.K = K; p.N = N;
     p.conv = conv;
+    p.at = at;
+    p.at_pitch = at_pitch;
     p.tiles_r = (M + C::RT - 1) / C::RT;
     p.tiles_c = (N + C::CT - 1) / C::CT;
     const long tiles = (long)p.tiles_r * p.tiles_c;
@@ -241,12 +255,12 @@ static int launch_fwd_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, cons
 }
 
 int forward_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K, int N,
-                 const ConvGeom &conv, int num_sms, cudaStream_t stream) {
+                 const ConvGeom &conv, const uint8_t *at, int at_pitch, int num_sms, cudaStream_t stream) {
     switch (bits) {
-        case 4: return launch_fwd_slab<4>(a, w, c, lut, M, K, N, conv, num_sms, stream);
-        case 6: return launch_fwd_slab<6>(a, w, c, lut, M, K, N, conv, num_sms, stream);
-        case 7: return launch_fwd_slab<7>(a, w, c, lut, M, K, N, conv, num_sms, stream);
-        case 8: return launch_fwd_slab<8>(a, w, c, lut, M, K, N, conv, num_sms, stream);
+        case 4: return launch_fwd_slab<4>(a, w, c, lut, M, K, N, conv, at, at_pitch, num_sms, stream);
+        case 6: return launch_fwd_slab<6>(a, w, c, lut, M, K, N, conv, at, at_pitch, num_sms, stream);
+        case 7: return launch_fwd_slab<7>(a, w, c, lut, M, K, N, conv, at, at_pitch, num_sms, stream);
+        case 8: return launch_fwd_slab<8>(a, w, c, lut, M, K, N, conv, at, at_pitch, num_sms, stream);
     }
     return LUTGEMM_E_BITS;
 }

@@ -99,7 +99,8 @@ class _AppConvLayer(torch.autograd.Function):
         qw = torch.clamp(torch.round(weight / s_w - z_w), 0.0, w_qmax)
         wmat = qw.reshape(Cout, -1).t().to(torch.uint8).contiguous()
         y = torch.empty((M, Cout), dtype=torch.uint32, device=x.device)
-        approx_ops.approx_conv2d_forward(codes, wmat, y, _ops_state.lut_appmult, kh, kw, stride, padding, dilation)
+        codes_t = approx_ops.approx_conv2d_forward(codes, wmat, y, _ops_state.lut_appmult, kh, kw, stride, padding,
+                                                   dilation)
         geom = (H, W, kh, kw, stride, padding, dilation)
         valid = _valid_taps(geom, x.device)                                   # [kh*kw, L]
         box = _window_sum(chansum, geom).reshape(M)
@@ -107,6 +108,7 @@ class _AppConvLayer(torch.autograd.Function):
         taps = valid.sum(dim=0) * float(Cin)
         out = approx_ops.conv2d_epilogue(y, box, sumw_t, taps, s_a, s_w, z_a, z_w, bias, L)
         ctx.save_for_backward(x, codes, wmat, weight, quant)
+        ctx.codes_t = codes_t  # transposed unfolded codes of the forward kernel: the grad_w kernel reuses them
         ctx.cfg = (a_qmax, w_qmax, stride, padding, dilation, Ho, Wo, bias is not None)
         return out.view(B, Ho, Wo, Cout).permute(0, 3, 1, 2)  # NCHW view of channels-last memory
 
@@ -124,7 +126,8 @@ class _AppConvLayer(torch.autograd.Function):
         gwmat = torch.empty(wmat.shape, dtype=torch.float32, device=gy.device) if need_w else None
         if need_x or need_w:
             approx_ops.approx_conv2d_backward(gy, codes, wmat, gcodes, gwmat, _ops_state.lut_grad_a, _ops_state.lut_grad_b,
-                                              kh, kw, stride, padding, dilation)
+                                              kh, kw, stride, padding, dilation, codes_t=ctx.codes_t if need_w else None)
+        ctx.codes_t = None
         geom = (H, W, kh, kw, stride, padding, dilation)
         gx = gw = gb = None
         if need_x:

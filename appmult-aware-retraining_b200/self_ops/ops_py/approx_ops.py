@@ -180,7 +180,7 @@ class ApproxConv2dFused(Function):
         if lut_appmult is None:
             raise RuntimeError("lookup tables are not initialised: call init_lookup_tables first")
         y = torch.empty((B * Ho * Wo, Cout), dtype=torch.uint32, device=input.device)
-        approx_ops.approx_conv2d_forward(x_u8, wmat, y, lut_appmult, kh, kw, stride, padding, dilation)
+        ctx.codes_t = approx_ops.approx_conv2d_forward(x_u8, wmat, y, lut_appmult, kh, kw, stride, padding, dilation)
         ctx.save_for_backward(x_u8, wmat)
         ctx.geom = (kh, kw, stride, padding, dilation, tuple(weight.shape), Ho, Wo)
         # rows are (b, oh, ow): an NCHW tensor in channels-last memory, no copy
@@ -197,7 +197,8 @@ class ApproxConv2dFused(Function):
         gw = torch.empty(wmat.shape, dtype=torch.float32, device=gy.device) if ctx.needs_input_grad[1] else None
         if gx is not None or gw is not None:
             approx_ops.approx_conv2d_backward(gy, x_u8, wmat, gx, gw, lut_grad_a, lut_grad_b, kh, kw, stride, padding,
-                                              dilation)
+                                              dilation, codes_t=ctx.codes_t if gw is not None else None)
+        ctx.codes_t = None
         return gx, (gw.t().reshape(wshape) if gw is not None else None), None, None, None
 
 

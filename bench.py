@@ -218,13 +218,15 @@ def run_ours(args, rank, world, local_rank):
         })
     scratch_bytes = lib.lutgemm_backward_scratch_bytes(bits, M, K, N)
     scratch = torch.empty(max(1, scratch_bytes), dtype=torch.uint8, device=dev)
+    fwd_ws_bytes = lib.lutgemm_forward_scratch_bytes(bits, M, K, N)  # transposed activation codes
+    fwd_ws = torch.empty(max(1, fwd_ws_bytes), dtype=torch.uint8, device=dev)
     # + the code transposition and the two block-reduce kernels of the slab path, or the split-M reduce kernel
-    launches_per_step = 3 + ((3 if bits >= 7 else 1) if scratch_bytes else 0)
+    launches_per_step = 3 + ((3 if bits >= 7 else 1) if scratch_bytes else 0) + (1 if fwd_ws_bytes else 0)
     stream = torch.cuda.current_stream(dev)
 
     def fwd(s):
-        rc = lib.lutgemm_forward(s["a"].data_ptr(), s["w"].data_ptr(), s["c"].data_ptr(), lf.data_ptr(), bits, M, K, N,
-                                 stream.cuda_stream)
+        rc = lib.lutgemm_forward_ws(s["a"].data_ptr(), s["w"].data_ptr(), s["c"].data_ptr(), lf.data_ptr(), bits, M, K, N,
+                                    fwd_ws.data_ptr() if fwd_ws_bytes else None, fwd_ws_bytes, stream.cuda_stream)
         assert rc == 0, lib.lutgemm_status_string(rc)
 
     def bwd_gw(s):

@@ -58,6 +58,16 @@ int lutgemm_forward(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint1
                     int M, int K, int N, void *stream);
 
 /*
+ * Forward with a workspace.  With `scratch` (lutgemm_forward_scratch_bytes() bytes, 16-byte aligned; 0 bytes
+ * means the kernel chosen for this shape has no use for it and NULL may be passed) the activation codes are
+ * first transposed into it ([K][M rounded up to 16] uint8) and the main kernel reads them from there with
+ * coalesced loads; results are identical to lutgemm_forward.  No counterpart in the reference.
+ */
+size_t lutgemm_forward_scratch_bytes(int bits, int M, int K, int N);
+int lutgemm_forward_ws(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K,
+                       int N, void *scratch, size_t scratch_bytes, void *stream);
+
+/*
  * Scratch bytes lutgemm_backward needs for a problem (0 when none is needed).  The weight-gradient
  * kernel splits its long reduction over M into slabs whose partial sums live in this buffer, followed
  * by a transposed copy of the activation codes.
@@ -111,6 +121,26 @@ int lutgemm_conv2d_backward(const float *gy, const uint8_t *x, const uint8_t *wm
                             const int16_t *lut_ga, const int16_t *lut_gw, int bits, int B, int C, int H, int W,
                             int Cout, int kh, int kw, int stride, int pad, int dil, void *scratch,
                             size_t scratch_bytes, void *stream);
+
+/*
+ * Convolution forward / backward sharing one transposed copy of the unfolded activation codes.
+ * lutgemm_conv2d_forward_ws: as lutgemm_conv2d_forward; with `scratch`
+ * (lutgemm_conv2d_forward_scratch_bytes() bytes, 16-byte aligned; 0 = not used for this shape) the uint8
+ * im2col is written there once, transposed ([C*kh*kw][B*Ho*Wo rounded up to 16]), instead of being gathered
+ * by every tile of the main kernel, and stays valid on return.
+ * lutgemm_conv2d_backward_ws: as lutgemm_conv2d_backward; `codes_t` (may be NULL) is that buffer as the
+ * forward pass of the same layer left it, which saves the weight-gradient kernel its own transposition.
+ * No counterpart in the reference (it materialises the unfolded activations in fp32, twice).
+ */
+size_t lutgemm_conv2d_forward_scratch_bytes(int bits, int B, int C, int H, int W, int Cout, int kh, int kw,
+                                            int stride, int pad, int dil);
+int lutgemm_conv2d_forward_ws(const uint8_t *x, const uint8_t *wmat, uint32_t *y, const uint16_t *lut, int bits, int B,
+                              int C, int H, int W, int Cout, int kh, int kw, int stride, int pad, int dil,
+                              void *scratch, size_t scratch_bytes, void *stream);
+int lutgemm_conv2d_backward_ws(const float *gy, const uint8_t *x, const uint8_t *wmat, float *gx, float *gw,
+                               const int16_t *lut_ga, const int16_t *lut_gw, int bits, int B, int C, int H, int W,
+                               int Cout, int kh, int kw, int stride, int pad, int dil, const uint8_t *codes_t,
+                               void *scratch, size_t scratch_bytes, void *stream);
 
 /*
  * Quantisation prologue of an approximate convolution layer, one pass:

@@ -356,3 +356,46 @@ def test_whole_layer_kernels_match_the_autograd_expression(dev, bits, monkeypatc
         if bias:
             assert torch.allclose(ref.bias.grad, new.bias.grad, rtol=1e-5, atol=1e-6)
         assert xn.grad.stride() == xn.stride()
+
+
+@pytest.mark.parametrize("bits", [7, 8])
+def test_workspace_entry_points_match_the_plain_ones(dev, bits):
+    """lutgemm_forward_ws (activation codes transposed into a workspace first) against lutgemm_forward, and
+    a convolution backward fed the forward pass's transposed codes against one that makes its own."""
+    import ctypes
+    import approx_ops
+    lib = approx_ops.library()
+    lf, la, lw = (torch.from_numpy(t).to(dev) for t in synth_wire(bits, seed=50 + bits))
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    # a shape the row-broadcast kernel takes has no use for a workspace
+    assert lib.lutgemm_forward_scratch_bytes(bits, 100, 64, 16) == 0
+    for s_, (M, K, N) in enumerate([(1024, 48, 64), (1000, 45, 120), (960, 31, 62)]):
+        a, w, _ = rand_problem(bits, M, K, N, seed=60 * bits + s_)
+        at, wt = torch.from_numpy(a).to(dev), torch.from_numpy(w).to(dev)
+        c0 = torch.zeros(M, N, dtype=torch.uint32, device=dev)
+        c1 = torch.zeros(M, N, dtype=torch.uint32, device=dev)
+        assert lib.lutgemm_forward(at.data_ptr(), wt.data_ptr(), c0.data_ptr(), lf.data_ptr(), bits, M, K, N, stream) == 0
+        nbytes = lib.lutgemm_forward_scratch_bytes(bits, M, K, N)
+        assert nbytes == K * ((M + 15) // 16 * 16)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        assert lib.lutgemm_forward_ws(at.data_ptr(), wt.data_ptr(), c1.data_ptr(), lf.data_ptr(), bits, M, K, N,
+                                      ws.data_ptr(), nbytes, stream) == 0
+        assert torch.equal(c0.view(torch.int32), c1.view(torch.int32))
+        assert torch.equal(ws.view(K, -1)[:, :M], at.t())            # the workspace holds the transposed codes
+        assert lib.lutgemm_forward_ws(at.data_ptr(), wt.data_ptr(), c1.data_ptr(), lf.data_ptr(), bits, M, K, N,
+                                      ws.data_ptr(), nbytes - 1, stream) == -4   # LUTGEMM_E_SCRATCH
+    B, Cin, H, W, Cout, k, st, p = 3, 16, 32, 32, 64, 3, 1, 1
+    rng = np.random.default_rng(7 + bits)
+    x = torch.from_numpy(rng.integers(0, 1 << bits, (B, Cin, H, W)).astype(np.uint8)).to(dev)
+    wm = torch.from_numpy(rng.integers(0, 1 << bits, (Cin * k * k, Cout)).astype(np.uint8)).to(dev)
+    M = B * H * W
+    y = torch.empty(M, Cout, dtype=torch.uint32, device=dev)
+    codes_t = approx_ops.approx_conv2d_forward(x, wm, y, lf, k, k, st, p, 1)
+    assert codes_t is not None and codes_t.numel() == Cin * k * k * M
+    gy = torch.randn(M, Cout, device=dev)
+    out = []
+    for given in (None, codes_t):
+        gx, gw = torch.empty(x.shape, device=dev), torch.empty(wm.shape, device=dev)
+        approx_ops.approx_conv2d_backward(gy, x, wm, gx, gw, la, lw, k, k, st, p, 1, codes_t=given)
+        out.append((gx, gw))
+    assert torch.equal(out[0][0], out[1][0]) and torch.equal(out[0][1], out[1][1])
