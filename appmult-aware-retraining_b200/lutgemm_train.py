@@ -23,7 +23,7 @@ import self_ops
 from lutgemm_dp import allreduce_grads_bucketed
 from lutgemm_layers import prepare
 from lutgemm_luts import synthetic_multiplier, window_difference_gradients
-from lutgemm_models import resnet18_cifar
+from lutgemm_models import MODELS
 
 
 def install_tables(device, bits: int, lut_file: str | None) -> None:
@@ -35,9 +35,10 @@ def install_tables(device, bits: int, lut_file: str | None) -> None:
         self_ops.set_lookup_tables(device, fp, ga, gb, bits)
 
 
-def build(device, bits: int, conv_impl: str = "layer", use_ste: bool = False, lr: float = 0.01, num_classes: int = 10):
+def build(device, bits: int, conv_impl: str = "layer", use_ste: bool = False, lr: float = 0.01, model_name: str = "resnet18"):
     torch.manual_seed(0)  # identical initial weights on every rank
-    model = resnet18_cifar(num_classes).to(device)
+    ctor, _, classes = MODELS[model_name]
+    model = ctor(classes).to(device)
     prepare(model, a_bits=bits, w_bits=bits, use_ste_gradient=use_ste, conv_impl=conv_impl)
     model = model.to(memory_format=torch.channels_last).train()
     opt = torch.optim.SGD(model.parameters(), lr=lr, momentum=0.9)
@@ -55,6 +56,7 @@ def train_step(model, opt, params, images, labels):
 
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--model", choices=sorted(MODELS), default="resnet18")
     ap.add_argument("--lut-file", default=None)
     ap.add_argument("--bits", type=int, default=7, choices=[4, 6, 7, 8])
     ap.add_argument("--batch", type=int, default=256, help="per-GPU batch")
@@ -69,13 +71,14 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     install_tables(device, args.bits, args.lut_file)
-    model, opt = build(device, args.bits, args.conv_impl, args.ste, args.lr)
+    model, opt = build(device, args.bits, args.conv_impl, args.ste, args.lr, args.model)
+    _, image_shape, classes = MODELS[args.model]
     params = [p for p in model.parameters() if p.requires_grad]
     g = torch.Generator().manual_seed(100 + rank)
     t0 = time.time()
     for step in range(args.steps):
-        images = torch.randn(args.batch, 3, 32, 32, generator=g).pin_memory().to(device, non_blocking=True)
-        labels = torch.randint(0, 10, (args.batch,), generator=g).pin_memory().to(device, non_blocking=True)
+        images = torch.randn(args.batch, *image_shape, generator=g).pin_memory().to(device, non_blocking=True)
+        labels = torch.randint(0, classes, (args.batch,), generator=g).pin_memory().to(device, non_blocking=True)
         loss = train_step(model, opt, params, images, labels)
         if rank == 0 and (step % 10 == 0 or step == args.steps - 1):
             print(f"step {step:4d}  loss {loss.item():.4f}  {world * args.batch * (step + 1) / (time.time() - t0):.0f} img/s",

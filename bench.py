@@ -406,14 +406,14 @@ def run_ours(args, rank, world, local_rank):
 # ------------------------------------------------------------------------------------------------
 # ResNet-18 (CIFAR shape) data-parallel training step
 # ------------------------------------------------------------------------------------------------
-def run_resnet18(args, rank, world, local_rank):
+def run_model(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
     import torch.nn.functional as F
 
     import approx_ops
     import self_ops
-    from lutgemm_models import lut_macs_per_image, resnet18_cifar
+    from lutgemm_models import MODELS, lut_macs_per_image
     from lutgemm_train import build, train_step
 
     if not torch.cuda.is_available():
@@ -426,13 +426,14 @@ def run_resnet18(args, rank, world, local_rank):
     bits, batch = args.bits, args.batch
     L, qa, qb = synthetic_wire_tables(bits, 0)
     self_ops.set_lookup_tables(dev, L, qa, qb, bits)
-    macs_img = lut_macs_per_image(resnet18_cifar(10).to(dev))
-    model, opt = build(dev, bits, conv_impl=args.conv_impl)
+    ctor, image_shape, classes = MODELS[args.workload]
+    macs_img = lut_macs_per_image(ctor(classes).to(dev), image_shape)
+    model, opt = build(dev, bits, conv_impl=args.conv_impl, model_name=args.workload)
     params = [p for p in model.parameters() if p.requires_grad]
     g = torch.Generator().manual_seed(100 + rank)
     nsets = 4
-    imgs_h = [torch.randn(batch, 3, 32, 32, generator=g).pin_memory() for _ in range(nsets)]
-    lbls_h = [torch.randint(0, 10, (batch,), generator=g).pin_memory() for _ in range(nsets)]
+    imgs_h = [torch.randn(batch, *image_shape, generator=g).pin_memory() for _ in range(nsets)]
+    lbls_h = [torch.randint(0, classes, (batch,), generator=g).pin_memory() for _ in range(nsets)]
     imgs_d = [t.to(dev) for t in imgs_h]
     lbls_d = [t.to(dev) for t in lbls_h]
 
@@ -486,11 +487,11 @@ def run_resnet18(args, rank, world, local_rank):
     value = world * batch * args.steps / (total_ms * 1e-3)
     macs_step = 3.0 * macs_img * batch
     line = {
-        "metric": "appmult_resnet18_train_throughput", "value": value, "unit": "img/s", "n_gpus": world,
+        "metric": f"appmult_{args.workload}_train_throughput", "value": value, "unit": "img/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "u16 table -> u32 (fwd) / f32 (bwd) accumulate, f32 elsewhere",
         "data": "synthetic",
-        "config": {"workload": f"ResNet-18 CIFAR-shape AppMult training step, {bits}-bit, batch {batch}/GPU, SGD",
+        "config": {"workload": f"{WORKLOAD_NAMES[args.workload]} AppMult training step, {bits}-bit, batch {batch}/GPU, SGD",
                    "bits": bits, "batch_per_gpu": batch, "conv_impl": args.conv_impl,
                    "lut_macs_per_step_per_gpu": macs_step,
                    "parallelism": f"dp{world} (batch sharded, bucketed NCCL all-reduce of gradients)" if world > 1 else "single GPU",
@@ -501,13 +502,18 @@ def run_resnet18(args, rank, world, local_rank):
                      "peak_def": f"{sms} SMs x {clk_max:.0f} MHz ({peaks_kind} sm_max_mhz) x 32 lookups/clk/SM", "traffic": None},
         "cpu_baseline": None,
         "e2e": {"value": world * batch * e2e_steps / (e2e_ms * 1e-3), "unit": "img/s",
-                "h2d_bytes_per_step": batch * (3 * 32 * 32 * 4 + 8), "d2h_bytes_per_step": 4, "steps": e2e_steps,
+                "h2d_bytes_per_step": batch * (int(np.prod(image_shape)) * 4 + 8), "d2h_bytes_per_step": 4, "steps": e2e_steps,
                 "ms_per_step": e2e_ms / e2e_steps, "last_loss": loss_value},
         "gpu_launches": None, "clocks": clocks, "device_error": err,
     }
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+WORKLOAD_NAMES = {"resnet18": "ResNet-18 CIFAR-shape", "resnet50": "ResNet-50 ImageNet-shape", "vit_s": "ViT-S/16"}
+# per-workload defaults of the benchmark configurations: (bits, per-GPU batch)
+WORKLOAD_DEFAULTS = {"resnet18": (7, 256), "resnet50": (8, 128), "vit_s": (7, 64)}
 
 
 def main():
@@ -519,8 +525,8 @@ def main():
     ap.add_argument("--bits", type=int, default=8, choices=[4, 6, 7, 8])
     ap.add_argument("--size", type=int, default=4096)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", choices=["lutgemm", "resnet18"], default="lutgemm")
-    ap.add_argument("--batch", type=int, default=256, help="per-GPU batch of the resnet18 workload")
+    ap.add_argument("--workload", choices=["lutgemm", "resnet18", "resnet50", "vit_s"], default="lutgemm")
+    ap.add_argument("--batch", type=int, default=None, help="per-GPU batch of the model workloads")
     ap.add_argument("--conv-impl", choices=["layer", "fused", "unfold"], default="layer")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -529,10 +535,12 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference_arm(args, rank, world)
-    elif args.workload == "resnet18":
+    elif args.workload != "lutgemm":
         if "--bits" not in sys.argv:
-            args.bits = 7
-        run_resnet18(args, rank, world, local_rank)
+            args.bits = WORKLOAD_DEFAULTS[args.workload][0]
+        if args.batch is None:
+            args.batch = WORKLOAD_DEFAULTS[args.workload][1]
+        run_model(args, rank, world, local_rank)
     else:
         run_ours(args, rank, world, local_rank)
 

@@ -134,3 +134,33 @@ def test_config4_vit_small_layer_shapes(dev, oracle_c):
     for s_, (K, N) in enumerate([(384, 1152), (384, 384), (384, 1536), (1536, 384)]):   # QKV, proj, MLP up / down
         _check_gemm(dev, oracle_c, bits, tokens, K, N, 400 + s_, tables)
     _check_conv(dev, oracle_c, bits, (1, 3, 224, 224, 384, 16, 16, 0), 450, tables)    # patch embedding
+
+
+@pytest.mark.parametrize("name,kw,shape,bits", [
+    ("resnet50", dict(base=8, blocks=(1, 1, 1, 1)), (2, 3, 64, 64), 8),
+    ("vit_s", dict(image=32, dim=48, depth=2, heads=3, mlp=96), (2, 3, 32, 32), 7)])
+def test_reduced_models_take_a_training_step(dev, name, kw, shape, bits):
+    """A narrow ResNet-50 (bottleneck blocks, 7x7 stem) and a small ViT (patch embedding, attention with exact
+    softmax, approximate linears) run forward, backward and an SGD step through the approximate layers."""
+    import self_ops
+    import torch.nn.functional as F
+    from lutgemm_layers import AppConv2d, AppLinear, prepare
+    from lutgemm_models import MODELS
+    fp, ga, gb = O.synthetic_tables(bits, seed=bits)
+    self_ops.set_lookup_tables(dev, fp, ga, gb, bits)
+    torch.manual_seed(0)
+    model = MODELS[name][0](10, **kw).to(dev)
+    prepare(model, a_bits=bits, w_bits=bits, conv_impl="layer")
+    assert any(isinstance(m, AppConv2d) for m in model.modules()) and any(isinstance(m, AppLinear) for m in model.modules())
+    opt = torch.optim.SGD(model.parameters(), lr=0.01)
+    x = torch.randn(*shape, device=dev)
+    y = torch.randint(0, 10, (shape[0],), device=dev)
+    losses = []
+    for _ in range(2):
+        opt.zero_grad(set_to_none=True)
+        loss = F.cross_entropy(model(x), y)
+        loss.backward()
+        assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters() if p.requires_grad)
+        opt.step()
+        losses.append(float(loss.detach()))
+    assert all(np.isfinite(losses))
