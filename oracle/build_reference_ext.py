@@ -29,6 +29,9 @@ def build(ref: str, bits: int) -> str:
     name = f"approx_ops_ref{bits}"
     so = os.path.join(OUT, name + sysconfig.get_config_var("EXT_SUFFIX"))
     os.makedirs(OUT, exist_ok=True)
+    srcs = [os.path.join(ref, "self_ops", "src", f) for f in FILES]
+    if os.path.exists(so) and os.path.getmtime(so) >= max(os.path.getmtime(f) for f in srcs + [__file__]):
+        return so  # up to date
     with tempfile.TemporaryDirectory() as tmp:
         for f in FILES:
             shutil.copy(os.path.join(ref, "self_ops", "src", f), tmp)
@@ -59,7 +62,9 @@ def build(ref: str, bits: int) -> str:
 
 if __name__ == "__main__":
     args = sys.argv[1:]
-    ref = args[0] if args and not args[0].isdigit() else "/root/reference"
+    ref = args[0] if args and not args[0].isdigit() else os.environ.get("APPMULT_REFERENCE", "")
+    if not os.path.isdir(ref):
+        raise SystemExit("usage: build_reference_ext.py REFERENCE_CHECKOUT [bits ...]  (or set APPMULT_REFERENCE)")
     widths = [int(a) for a in args if a.isdigit()] or [7, 8]
     for b in widths:
         print(build(ref, b))

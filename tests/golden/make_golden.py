@@ -20,7 +20,9 @@ import types
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("APPMULT_REFERENCE", "")
+if not os.path.isdir(REF):
+    raise SystemExit("usage: make_golden.py REFERENCE_CHECKOUT  (or set APPMULT_REFERENCE)")
 OUT = os.path.dirname(os.path.abspath(__file__))
 
 LUT_FILES = {
