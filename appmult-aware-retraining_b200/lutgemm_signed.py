@@ -30,6 +30,20 @@ def _pack(dense: np.ndarray, bits: int, dtype) -> np.ndarray:
     return flat
 
 
+def signed_dense_tables(fp: np.ndarray, grad_a: np.ndarray, grad_b: np.ndarray):
+    """Dense [2Q, 2Q] tables of the codes `sign << b | magnitude`: (forward + offset, round(16 d/da), round(16 d/dw),
+    offset) with offset = max(fp)."""
+    fp = np.asarray(fp, dtype=np.int64)
+    q = fp.shape[0]
+    offset = int(fp.max())
+    sign = np.concatenate([np.ones(q, np.int64), -np.ones(q, np.int64)])
+    big = lambda t: np.tile(np.asarray(t), (2, 2))  # index (sign << b | magnitude) in both directions
+    fp_s = sign[:, None] * sign[None, :] * big(fp) + offset
+    ga_s = sign[None, :] * np.round(big(np.asarray(grad_a, np.float64)) * _GRAD_SCALE).astype(np.int64)
+    gb_s = sign[:, None] * np.round(big(np.asarray(grad_b, np.float64)) * _GRAD_SCALE).astype(np.int64)
+    return fp_s, ga_s, gb_s, offset
+
+
 class SignedTables:
     """Device tables of the signed operator built from magnitude tables fp [2^b, 2^b] (non-negative integers),
     grad_a / grad_b (floats, d product / d magnitude)."""
@@ -42,12 +56,7 @@ class SignedTables:
         if fp.shape != (q, q) or fp.min() < 0 or 2 * int(fp.max()) > 0xFFFF:
             raise ValueError("forward table must be [2^b, 2^b], non-negative, with 2*max <= 65535")
         self.magnitude_bits, self.kernel_bits = magnitude_bits, _MAG_TO_KERNEL_BITS[magnitude_bits]
-        self.offset = int(fp.max())
-        sign = np.concatenate([np.ones(q, np.int64), -np.ones(q, np.int64)])
-        big = lambda t: np.tile(np.asarray(t), (2, 2))  # index (sign << b | magnitude) in both directions
-        fp_s = sign[:, None] * sign[None, :] * big(fp) + self.offset
-        ga_s = sign[None, :] * np.round(big(np.asarray(grad_a, np.float64)) * _GRAD_SCALE).astype(np.int64)
-        gb_s = sign[:, None] * np.round(big(np.asarray(grad_b, np.float64)) * _GRAD_SCALE).astype(np.int64)
+        fp_s, ga_s, gb_s, self.offset = signed_dense_tables(fp, grad_a, grad_b)
         for t in (ga_s, gb_s):
             if t.min() < -32768 or t.max() > 32767:
                 raise ValueError("gradient table does not fit the 16-bit wire format")
