@@ -146,6 +146,60 @@ class _AppConvLayer(torch.autograd.Function):
         return gx, gw, gb, None, None, None, None, None, None
 
 
+class _AppLinearLayer(torch.autograd.Function):
+    """The whole approximate linear layer: quantisation prologue, LUT-GEMM, de-quantisation epilogue with the
+    zero-point cross terms (one output position, so the window sums are a row sum of the activation codes, a
+    column sum of the weight codes and K), and their backward.  Same values and gradients as the expression
+    in `AppLinear.forward` evaluated by autograd."""
+
+    @staticmethod
+    def forward(ctx, x2, weight, bias, quant, a_qmax, w_qmax):
+        if _ops_state.lut_appmult is None:
+            raise RuntimeError("lookup tables are not initialised: call init_lookup_tables first")
+        s_a, z_a, s_w, z_w = (quant[i:i + 1] for i in range(4))
+        M, K = x2.shape
+        N = weight.shape[0]
+        x2 = x2.contiguous()
+        # rows as the channel dimension of a one-row image: the kernel's 32 x 32 tiles are then all payload
+        codes, _ = approx_ops.quantize_activations(x2.view(1, M, 1, K), s_a, z_a, a_qmax, want_chansum=False)
+        codes = codes.view(M, K)
+        qw = torch.clamp(torch.round(weight / s_w - z_w), 0.0, w_qmax)
+        wmat = qw.t().to(torch.uint8).contiguous()
+        y = torch.empty((M, N), dtype=torch.uint32, device=x2.device)
+        approx_ops.approx_gemm_forward(codes, wmat, y, _ops_state.lut_appmult)
+        box = codes.sum(dim=1, dtype=torch.float32)
+        sumw_t = qw.sum(dim=1).view(1, N).contiguous()
+        taps = torch.full((1,), float(K), device=x2.device)
+        out = approx_ops.conv2d_epilogue(y, box, sumw_t, taps, s_a, s_w, z_a, z_w, bias, 1)
+        ctx.save_for_backward(x2, codes, wmat, weight, quant)
+        ctx.cfg = (a_qmax, w_qmax, bias is not None)
+        return out
+
+    @staticmethod
+    def backward(ctx, g_out):
+        x2, codes, wmat, weight, quant = ctx.saved_tensors
+        a_qmax, w_qmax, has_bias = ctx.cfg
+        s_a, z_a, s_w, z_w = (quant[i:i + 1] for i in range(4))
+        M, K = x2.shape
+        gy = g_out.contiguous()
+        need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        ga = torch.empty((M, K), dtype=torch.float32, device=gy.device)
+        gw = torch.empty(wmat.shape, dtype=torch.float32, device=gy.device)
+        approx_ops.approx_gemm_backward(gy, codes, wmat, ga, gw, _ops_state.lut_grad_a, _ops_state.lut_grad_b)
+        gx = gwt = gb = None
+        if need_x:
+            ga.add_(z_w * gy.sum(dim=1, keepdim=True))  # cross term z_w * rowsum(q_a)
+            gx = approx_ops.quantize_activations_backward(x2.view(1, M, 1, K), s_a, z_a, a_qmax, ga.view(1, M, 1, K),
+                                                          None, s_w, z_w).view(M, K)
+        if need_w:
+            g_qw = gw.t() + z_a * gy.sum(dim=0).unsqueeze(1)  # cross term z_a * colsum(q_w)
+            q = torch.round(weight / s_w - z_w)
+            gwt = torch.where((q >= 0) & (q <= w_qmax), s_a * g_qw, torch.zeros_like(g_qw))
+        if has_bias and ctx.needs_input_grad[2]:
+            gb = gy.sum(dim=0)
+        return gx, gwt, gb, None, None, None
+
+
 class _MinMax(nn.Module):
     """Running min/max (weights) or exponential moving average of min/max (activations)."""
 
@@ -245,15 +299,21 @@ class AppConv2d(nn.Conv2d, _AppQuant):
 
 
 class AppLinear(nn.Linear, _AppQuant):
-    def __init__(self, in_features, out_features, bias=True, a_bits=7, w_bits=7, use_ste_gradient=False):
+    def __init__(self, in_features, out_features, bias=True, a_bits=7, w_bits=7, use_ste_gradient=False,
+                 impl="ops"):
         nn.Linear.__init__(self, in_features, out_features, bias)
         self._init_quant(a_bits, w_bits)
         self.use_ste_gradient = use_ste_gradient
+        self.impl = impl  # "ops": PyTorch quantisation around the LUT-GEMM op; "layer": the whole-layer kernels
 
     def forward(self, x):
         self._refresh(x, self.weight)
         lead = x.shape[:-1]
         x2 = x.reshape(-1, self.in_features)
+        if self.impl == "layer" and not self.use_ste_gradient and x.is_cuda:
+            quant = torch.cat([self.activation_scale, self.activation_zp_neg, self.weight_scale, self.weight_zp_neg])
+            out = _AppLinearLayer.apply(x2, self.weight, self.bias, quant, self.a_qmax, self.w_qmax)
+            return out.reshape(*lead, self.out_features)
         xq = self._codes(x2, self.activation_scale, self.activation_zp_neg, self.a_qmax)
         wq = self._codes(self.weight, self.weight_scale, self.weight_zp_neg, self.w_qmax)
         gemm = self_ops.approx_gemm_baseline_op if self.use_ste_gradient else self_ops.approx_gemm_op
@@ -281,7 +341,8 @@ def prepare(model: nn.Module, a_bits: int = 7, w_bits: int = 7, use_ste_gradient
             new.bias = child.bias
             setattr(model, name, new.to(child.weight.device))
         elif linear and isinstance(child, nn.Linear):
-            new = AppLinear(child.in_features, child.out_features, child.bias is not None, a_bits, w_bits, use_ste_gradient)
+            new = AppLinear(child.in_features, child.out_features, child.bias is not None, a_bits, w_bits, use_ste_gradient,
+                            "layer" if conv_impl == "layer" else "ops")
             new.weight = child.weight
             new.bias = child.bias
             setattr(model, name, new.to(child.weight.device))
