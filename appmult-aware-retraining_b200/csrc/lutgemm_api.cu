@@ -66,7 +66,10 @@ BackwardPlan plan_backward(int bits, int M, int K, int N, int sms) {
     // (11.5 / 11.6) beat the slab kernels.  grad_a needs N >= 768 for a slab: on convolution shapes with
     // N <= 512 the column-broadcast kernel is faster at both 7 and 8 bits.
     pl.gw_slab = bits >= 7 && M >= 512 && N >= 32 && slab_fill(M, N) >= 0.6;
-    pl.ga_slab = bits >= 7 && N >= 768 && M >= 32 && slab_fill(N, M) >= 0.6;
+    // (a partly filled slab tile only pays against the column-broadcast kernel, which runs at about 37 % of the
+    // roofline at 7 bits and 29 % at 8 bits whatever N is, when the better of the two tilings is this full)
+    const double ga_fill = slab_fill(N, M) > tall_fill(N, M) ? slab_fill(N, M) : tall_fill(N, M);
+    pl.ga_slab = bits >= 7 && N >= 768 && M >= 32 && ga_fill >= (bits == 7 ? 0.85 : 0.7);
     if (env_is("LUTGEMM_BACKWARD_KERNEL", "bcast")) pl.gw_slab = pl.ga_slab = false;
     if (env_is("LUTGEMM_BACKWARD_KERNEL", "slab")) pl.gw_slab = pl.ga_slab = true;
     pl.gw_tall = pl.gw_slab && tall_fill(M, N) >= 0.85 * slab_fill(M, N);
