@@ -18,9 +18,12 @@
 // The two halves of a slab word go to the accumulators as  S += word,  H += word >> 16 ; at the end
 // sum(lo) = S - (H << 16) (mod 2^32) and sum(hi) = H.
 // Work items are (tile, K split); splits of one tile are combined with integer atomics, which are
-// exact in any order, so the result stays bit-identical.  With conv.enabled the activation codes are
-// gathered from the NCHW code image on the fly (implicit im2col).
-// The gradient kernels built on the same idea are in lutgemm_slab_grad.cu.
+// exact in any order, so the result stays bit-identical.  The activation codes come either from a
+// transposed copy at[k][m] in a workspace (16 rows of one k per 16-byte load, coalesced; for a convolution
+// that copy is the uint8 im2col, made once) or, without a workspace, straight from a[m][k] - with
+// conv.enabled gathered from the NCHW code image on the fly (implicit im2col) - and transposed byte-wise
+// on their way into shared memory.
+// The gradient kernels built on the same idea are in lutgemm_slab_grad_tall.cu and lutgemm_slab_grad.cu.
 // Replaces ApproxGemmForwardKernel, self_ops/src/approx_gemm_forward.cu:37-229.
 #include "lutgemm_common.cuh"
 #include "lutgemm_kernels.h"

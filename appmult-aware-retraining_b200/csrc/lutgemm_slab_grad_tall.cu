@@ -13,6 +13,9 @@
 // while slab k is read and one CTA barrier per k suffices at every bit-width.
 // Partial sums: one per lane, warp and k; the 16 warps are added in ascending order by one warp (rotating
 // with k), row blocks by slab_reduce_blocks in ascending order: results are deterministic.
+// grad_w takes its row codes from a transposed copy at[k][m] of the activation codes when the caller has one
+// (lutgemm_api.cu makes it, or receives the forward pass's): the same coalesced 16-byte fetch as grad_a's
+// weight rows instead of one 16-byte piece per activation row.
 // Used when the reduction dimension fills 1024-row tiles well; otherwise the 512 x 64 kernel runs.
 // Replaces ApproxGemmBackwardKernelForGA / ForGB, self_ops/src/approx_gemm_backward.cu:13-258, 261-492.
 #include "lutgemm_common.cuh"
