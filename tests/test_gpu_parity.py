@@ -399,3 +399,48 @@ def test_workspace_entry_points_match_the_plain_ones(dev, bits):
         approx_ops.approx_conv2d_backward(gy, x, wm, gx, gw, la, lw, k, k, st, p, 1, codes_t=given)
         out.append((gx, gw))
     assert torch.equal(out[0][0], out[1][0]) and torch.equal(out[0][1], out[1][1])
+
+
+@pytest.mark.parametrize("bits", [4, 6, 7, 8])
+def test_random_shapes_through_the_dispatcher(dev, oracle_c, bits):
+    """Seeded random shapes (tile edges, ragged K, rows and columns that are not multiples of anything) through
+    whatever kernels the dispatcher picks, GEMM and convolution, against the oracle."""
+    import approx_ops
+    lf, la, lw = synth_wire(bits, seed=90 + bits)
+    rng = np.random.default_rng(9000 + bits)
+    shapes = []
+    while len(shapes) < 14:
+        M, K, N = (int(v) for v in np.exp(rng.uniform(0, np.log(2600), 3)))
+        if M * K * N <= 40_000_000:
+            shapes.append((M, K, N))
+    shapes += [(1030, 17, 33), (2049, 5, 70), (1023, 100, 31), (3000, 9, 800), (40, 60, 1025), (1024, 16, 32)]
+    for s_, (M, K, N) in enumerate(shapes):
+        a, w, gc = rand_problem(bits, M, K, N, seed=31 * bits + s_)
+        c = run_forward(dev, a, w, lf)
+        assert np.array_equal(c, oracle_c.forward(a, w, lf, bits)), (bits, M, K, N)
+        ga, gw = run_backward(dev, gc, a, w, la, lw)
+        check_backward(oracle_c, gc, a, w, la, lw, bits, ga, gw)
+    lft, lat, lwt = (torch.from_numpy(t).to(dev) for t in (lf, la, lw))
+    for s_ in range(8):
+        B, Cin, Cout = int(rng.integers(1, 5)), int(rng.integers(1, 40)), int(rng.integers(1, 90))
+        k, st, d = int(rng.choice([1, 2, 3, 5])), int(rng.choice([1, 2, 3])), int(rng.choice([1, 2]))
+        p = int(rng.integers(0, k))
+        H, W = int(rng.integers(d * (k - 1) + 1, 40)), int(rng.integers(d * (k - 1) + 1, 40))
+        x = rng.integers(0, 1 << bits, (B, Cin, H, W)).astype(np.uint8)
+        wmat = rng.integers(0, 1 << bits, (Cin * k * k, Cout)).astype(np.uint8)
+        Ho, Wo = (H + 2 * p - d * (k - 1) - 1) // st + 1, (W + 2 * p - d * (k - 1) - 1) // st + 1
+        gy = rng.standard_normal((B * Ho * Wo, Cout)).astype(np.float32)
+        col = oracle_c.im2col(x, k, k, st, p, d)
+        xt, wm = torch.from_numpy(x).to(dev), torch.from_numpy(wmat).to(dev)
+        y = torch.empty((B * Ho * Wo, Cout), dtype=torch.uint32, device=dev)
+        codes_t = approx_ops.approx_conv2d_forward(xt, wm, y, lft, k, k, st, p, d)
+        assert np.array_equal(y.cpu().numpy(), oracle_c.forward(col, wmat, lf, bits)), (bits, B, Cin, H, W, Cout, k, st, p, d)
+        gx = torch.full(x.shape, float("nan"), dtype=torch.float32, device=dev)
+        gw = torch.full(wmat.shape, float("nan"), dtype=torch.float32, device=dev)
+        approx_ops.approx_conv2d_backward(torch.from_numpy(gy).to(dev), xt, wm, gx, gw, lat, lwt, k, k, st, p, d,
+                                          codes_t=codes_t)
+        r_ga, r_gw, r_gaa, r_gwa = oracle_c.backward_f64(gy, col, wmat, la, lw, bits)
+        assert (np.abs(gw.cpu().numpy() - r_gw) <= TOL * r_gwa + 1e-30).all(), (bits, B, Cin, H, W, Cout, k, st, p, d)
+        r_gx = O.col2im_f64(r_ga, x.shape, k, k, st, p, d)
+        r_gxa = O.col2im_f64(r_gaa, x.shape, k, k, st, p, d)
+        assert (np.abs(gx.cpu().numpy() - r_gx) <= TOL * r_gxa + 1e-30).all(), (bits, B, Cin, H, W, Cout, k, st, p, d)
