@@ -98,3 +98,45 @@ def write_lut_file(path: str, fp: np.ndarray, grad_a: np.ndarray, grad_b: np.nda
             f.write(title + "\n")
             rows = np.stack([a.ravel(), b.ravel(), np.asarray(t, np.int64).ravel()], axis=1)
             f.write("\n".join(" ".join(map(str, r)) for r in rows.tolist()) + "\n")
+
+
+def load_lut_file(path: str, bits: int, cache: bool = True):
+    """Three dense int64 [2^b, 2^b] tables (forward, d/da * 16, d/db * 16) from a LUT text file, with a binary
+    cache beside it: parsing a 8-bit file means 196 608 text lines, the cache (`<file>.b<bits>.npz`, rewritten
+    whenever the text file is newer) loads in milliseconds.  The `INFO:` header's mean error distance, when
+    present, is checked against the parsed forward table."""
+    import os
+    import re
+    cache_path = f"{path}.b{bits}.npz"
+    if cache and os.path.exists(cache_path) and os.path.getmtime(cache_path) >= os.path.getmtime(path):
+        z = np.load(cache_path)
+        return z["fp"], z["grad_a"], z["grad_b"]
+    q = 1 << bits
+    tables = [np.zeros((q, q), np.int64) for _ in range(3)]
+    section, med = -1, None
+    with open(path) as f:
+        for line in f:
+            line = line.strip()
+            if line in TITLES:
+                section = TITLES.index(line)
+                continue
+            if section < 0:
+                m = re.search(r"Mean error distance[^:]*:\s*([0-9.eE+-]+)", line)
+                if m:
+                    med = float(m.group(1))
+                continue
+            parts = line.split()
+            if len(parts) == 3:
+                a, b, v = int(parts[0]), int(parts[1]), int(parts[2])
+                if a < q and b < q:
+                    tables[section][a, b] = v
+    if section != 2:
+        raise ValueError(f"{path}: expected three table sections, found {section + 1}")
+    if med is not None and abs(error_metrics(tables[0])["med"] - med) > 1e-3 * max(1.0, med):
+        raise ValueError(f"{path}: header mean error distance {med} does not match the table")
+    if cache:
+        try:
+            np.savez(cache_path, fp=tables[0], grad_a=tables[1], grad_b=tables[2])
+        except OSError:
+            pass  # read-only location: just skip the cache
+    return tuple(tables)

@@ -54,6 +54,20 @@ def train_step(model, opt, params, images, labels):
     return loss
 
 
+@torch.no_grad()
+def evaluate(model, batches):
+    """Top-1 accuracy over (images, labels) batches, without building autograd graphs (the reference's test loop
+    runs with gradients enabled, micronet+/app_train.py:39-85); observers are frozen by eval()."""
+    was_training = model.training
+    model.eval()
+    correct = total = 0
+    for images, labels in batches:
+        correct += int((model(images).argmax(dim=1) == labels).sum())
+        total += labels.numel()
+    model.train(was_training)
+    return correct / max(1, total)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", choices=sorted(MODELS), default="resnet18")
@@ -64,6 +78,7 @@ def main():
     ap.add_argument("--lr", type=float, default=0.01)
     ap.add_argument("--ste", action="store_true", help="straight-through backward instead of the gradient tables")
     ap.add_argument("--conv-impl", choices=["layer", "fused", "unfold"], default="layer")
+    ap.add_argument("--eval-batches", type=int, default=0, help="synthetic batches to evaluate after training")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     device = torch.device(f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}")
@@ -83,6 +98,12 @@ def main():
         if rank == 0 and (step % 10 == 0 or step == args.steps - 1):
             print(f"step {step:4d}  loss {loss.item():.4f}  {world * args.batch * (step + 1) / (time.time() - t0):.0f} img/s",
                   flush=True)
+    if args.eval_batches:
+        data = [(torch.randn(args.batch, *image_shape, generator=g).to(device),
+                 torch.randint(0, classes, (args.batch,), generator=g).to(device)) for _ in range(args.eval_batches)]
+        acc = evaluate(model, data)
+        if rank == 0:
+            print(f"eval accuracy on {args.eval_batches} synthetic batches: {acc:.4f}", flush=True)
     if world > 1:
         dist.destroy_process_group()
 

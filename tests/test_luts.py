@@ -47,3 +47,25 @@ def test_error_metrics_match_the_reference_header():
     g = load_golden("mult7_med63")
     m = LU.error_metrics(O.unpack_padded(g["lut_fp"], 7))
     assert abs(m["med"] - 63.5938720703125) < 1e-9 and abs(m["mse"] - 9228.21875) < 1e-6 and m["max_ed"] == 713.0
+
+
+def test_load_lut_file_parses_caches_and_checks_the_header(tmp_path):
+    import lutgemm_luts as L
+    bits = 6
+    fp = L.synthetic_multiplier(bits, seed=5)
+    ga, gb = L.window_difference_gradients(fp, 4)
+    path = str(tmp_path / "lut.txt")
+    L.write_lut_file(path, fp, ga, gb)
+    t1 = L.load_lut_file(path, bits)
+    assert all(np.array_equal(x, y) for x, y in zip(t1, (fp, ga, gb)))
+    import os
+    assert os.path.exists(path + f".b{bits}.npz")
+    t2 = L.load_lut_file(path, bits)  # from the cache
+    assert all(np.array_equal(x, y) for x, y in zip(t2, (fp, ga, gb)))
+    # a header that does not match the table is refused
+    text = open(path).read().replace("Mean error distance between lut_appmult and lut_mult: ", "Mean error distance between lut_appmult and lut_mult: 9")
+    bad = str(tmp_path / "bad.txt")
+    open(bad, "w").write(text)
+    import pytest
+    with pytest.raises(ValueError, match="does not match"):
+        L.load_lut_file(bad, bits, cache=False)
