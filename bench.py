@@ -428,7 +428,7 @@ def run_model(args, rank, world, local_rank):
     self_ops.set_lookup_tables(dev, L, qa, qb, bits)
     ctor, image_shape, classes = MODELS[args.workload]
     macs_img = lut_macs_per_image(ctor(classes).to(dev), image_shape)
-    model, opt = build(dev, bits, conv_impl=args.conv_impl, model_name=args.workload)
+    model, opt = build(dev, bits, conv_impl=args.conv_impl, use_ste=args.ste, model_name=args.workload)
     params = [p for p in model.parameters() if p.requires_grad]
     g = torch.Generator().manual_seed(100 + rank)
     nsets = 4
@@ -492,7 +492,7 @@ def run_model(args, rank, world, local_rank):
         "scaling": "weak", "vs_baseline": None, "dtype": "u16 table -> u32 (fwd) / f32 (bwd) accumulate, f32 elsewhere",
         "data": "synthetic",
         "config": {"workload": f"{WORKLOAD_NAMES[args.workload]} AppMult training step, {bits}-bit, batch {batch}/GPU, SGD",
-                   "bits": bits, "batch_per_gpu": batch, "conv_impl": args.conv_impl,
+                   "bits": bits, "batch_per_gpu": batch, "conv_impl": args.conv_impl, "ste_backward": bool(args.ste),
                    "lut_macs_per_step_per_gpu": macs_step,
                    "parallelism": f"dp{world} (batch sharded, bucketed NCCL all-reduce of gradients)" if world > 1 else "single GPU",
                    "l2": f"{nsets} rotating batches; activations of a step exceed L2"},
@@ -528,6 +528,7 @@ def main():
     ap.add_argument("--workload", choices=["lutgemm", "resnet18", "resnet50", "vit_s"], default="lutgemm")
     ap.add_argument("--batch", type=int, default=None, help="per-GPU batch of the model workloads")
     ap.add_argument("--conv-impl", choices=["layer", "fused", "unfold"], default="layer")
+    ap.add_argument("--ste", action="store_true", help="model workloads: straight-through backward instead of the gradient tables")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
