@@ -269,7 +269,9 @@ class AppConv2d(nn.Conv2d, _AppQuant):
     def _approx_conv(self, xq, wq):
         kw = dict(bias=None, stride=self.stride, padding=self.padding, dilation=self.dilation, groups=1)
         if self.use_ste_gradient:
-            return self_ops.approx_conv2d_baseline_op(xq, wq, **kw)
+            if self.conv_impl == "unfold":
+                return self_ops.approx_conv2d_baseline_op(xq, wq, **kw)
+            return self_ops.approx_conv2d_fused_baseline_op(xq, wq, **kw)
         if self.conv_impl == "fused":
             return self_ops.approx_conv2d_fused_op(xq, wq, **kw)
         return self_ops.approx_conv2d_op(xq, wq, **kw)

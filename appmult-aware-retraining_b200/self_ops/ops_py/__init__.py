@@ -6,6 +6,7 @@ from .approx_ops import (
     approx_conv2d_op,
     approx_conv2d_baseline_op,
     approx_conv2d_fused_op,
+    approx_conv2d_fused_baseline_op,
 )
 
 # the first five names are the reference's public API (self_ops/ops_py/__init__.py:1-12)
@@ -17,4 +18,5 @@ __all__ = [
     "approx_conv2d_baseline_op",
     "set_lookup_tables",
     "approx_conv2d_fused_op",
+    "approx_conv2d_fused_baseline_op",
 ]

@@ -207,3 +207,44 @@ def approx_conv2d_fused_op(input, weight, bias, stride, padding, dilation, group
     assert bias is None, "bias is not supported in approximate convolution"
     assert groups == 1, "groups is not supported in approximate convolution"
     return ApproxConv2dFused.apply(input, weight, stride[0], padding[0], dilation[0])
+
+
+class ApproxConv2dFusedBaseline(Function):
+    """Straight-through variant of `ApproxConv2dFused`: the same fused LUT forward; the backward treats the
+    product as exact, i.e. the plain convolution gradients on the float codes (what `approx_conv2d_baseline_op`
+    computes through unfold + matmul, self_ops/ops_py/approx_ops.py:576-619 of the reference)."""
+
+    @staticmethod
+    def forward(ctx, input, weight, stride, padding, dilation):
+        B, Cin, H, W = input.shape
+        Cout, _, kh, kw = weight.shape
+        x_u8 = input.to(torch.uint8).contiguous()
+        wmat = weight.reshape(Cout, -1).t().to(torch.uint8).contiguous()
+        Ho = (H + 2 * padding - dilation * (kh - 1) - 1) // stride + 1
+        Wo = (W + 2 * padding - dilation * (kw - 1) - 1) // stride + 1
+        if lut_appmult is None:
+            raise RuntimeError("lookup tables are not initialised: call init_lookup_tables first")
+        y = torch.empty((B * Ho * Wo, Cout), dtype=torch.uint32, device=input.device)
+        approx_ops.approx_conv2d_forward(x_u8, wmat, y, lut_appmult, kh, kw, stride, padding, dilation)
+        ctx.save_for_backward(input, weight)
+        ctx.geom = (stride, padding, dilation)
+        return y.to(torch.float32).view(B, Ho, Wo, Cout).permute(0, 3, 1, 2)
+
+    @staticmethod
+    def backward(ctx, g_out):
+        input, weight = ctx.saved_tensors
+        stride, padding, dilation = ctx.geom
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            gx = torch.nn.grad.conv2d_input(input.shape, weight, g_out, stride=stride, padding=padding, dilation=dilation)
+        if ctx.needs_input_grad[1]:
+            gw = torch.nn.grad.conv2d_weight(input, weight.shape, g_out, stride=stride, padding=padding, dilation=dilation)
+        return gx, gw, None, None, None
+
+
+def approx_conv2d_fused_baseline_op(input, weight, bias, stride, padding, dilation, groups):
+    """Drop-in for `approx_conv2d_baseline_op` (same arguments and results up to fp32 summation order) with the
+    fused forward kernels."""
+    assert bias is None, "bias is not supported in approximate convolution"
+    assert groups == 1, "groups is not supported in approximate convolution"
+    return ApproxConv2dFusedBaseline.apply(input, weight, stride[0], padding[0], dilation[0])

@@ -444,3 +444,26 @@ def test_random_shapes_through_the_dispatcher(dev, oracle_c, bits):
         r_gx = O.col2im_f64(r_ga, x.shape, k, k, st, p, d)
         r_gxa = O.col2im_f64(r_gaa, x.shape, k, k, st, p, d)
         assert (np.abs(gx.cpu().numpy() - r_gx) <= TOL * r_gxa + 1e-30).all(), (bits, B, Cin, H, W, Cout, k, st, p, d)
+
+
+def test_fused_straight_through_op_matches_the_unfold_one(dev, golden):
+    """approx_conv2d_fused_baseline_op against approx_conv2d_baseline_op: identical forward (the LUT sums),
+    straight-through gradients equal to fp32 rounding."""
+    import self_ops
+    bits = int(golden["bits"])
+    fp, ga_t, gb_t = (O.unpack_padded(golden[k], bits) for k in ("lut_fp", "lut_ga", "lut_gb"))
+    self_ops.set_lookup_tables(dev, fp, ga_t, gb_t, bits)
+    for i in range(4):
+        B, Cin, H, W, Cout, k, s, p, d = [int(v) for v in golden[f"conv{i}_cfg"]]
+        kw = dict(bias=None, stride=(s, s), padding=(p, p), dilation=(d, d), groups=1)
+        outs = []
+        for op in (self_ops.approx_conv2d_baseline_op, self_ops.approx_conv2d_fused_baseline_op):
+            x = torch.from_numpy(golden[f"conv{i}_x"]).to(dev).float().requires_grad_(True)
+            wt = torch.from_numpy(golden[f"conv{i}_w"]).to(dev).float().requires_grad_(True)
+            y = op(x, wt, **kw)
+            y.backward(torch.from_numpy(golden[f"conv{i}_gy"]).to(dev))
+            outs.append((y.detach(), x.grad, wt.grad))
+        assert torch.equal(outs[0][0], outs[1][0])
+        assert np.array_equal(outs[1][0].cpu().numpy(), golden[f"conv{i}_y"])
+        for a_, b_ in zip(outs[0][1:], outs[1][1:]):
+            assert torch.allclose(a_, b_, rtol=2e-3, atol=1e-3 * float(a_.abs().max()))
