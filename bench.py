@@ -194,7 +194,9 @@ def run_ours(args, rank, world, local_rank):
         dist.init_process_group("nccl", device_id=dev)
 
     bits, S = args.bits, args.size
-    M = K = N = S
+    K = N = S
+    # weak scaling (default): every rank its own S rows; --shard-m: the S rows of one problem cut across the ranks
+    M = (S + world - 1) // world if args.shard_m else S
     L, qa, qb = synthetic_wire_tables(bits, 0)
     lf = torch.from_numpy(pack_wire(L, bits, np.uint16)).to(dev)
     la = torch.from_numpy(pack_wire(qa, bits, np.int16)).to(dev)
@@ -372,7 +374,7 @@ def run_ours(args, rank, world, local_rank):
         # dram__bytes_read.sum + dram__bytes_write.sum per launch of that kernel from the ncu capture
         # summarised in profiles/slab_kernels_b8_4096.md (only that configuration was captured)
         "traffic": ({"forward": 117.7e6, "grad_w": 360.9e6, "grad_a": 359.2e6}[names[dom]]
-                    if (bits, S) == (8, 4096) else None),
+                    if (bits, S, M) == (8, 4096, 4096) else None),
         "traffic_unit": "bytes per launch (ncu, 8-bit 4096^3)",
     }
 
@@ -387,9 +389,11 @@ def run_ours(args, rank, world, local_rank):
     line = {
         "metric": "lut_gemm_fwd_bwd_throughput", "value": value, "unit": "G LUT-MAC/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "u16 table -> u32 (fwd) / f32 (bwd) accumulate",
+        "scaling": "strong" if args.shard_m else "weak", "vs_baseline": None,
+        "dtype": "u16 table -> u32 (fwd) / f32 (bwd) accumulate",
         "data": "synthetic",
-        "config": {"workload": f"lutgemm fwd+bwd {bits}-bit M=K=N={S} per GPU", "bits": bits, "M_per_gpu": M, "K": K,
+        "config": {"workload": (f"lutgemm fwd+bwd {bits}-bit M=K=N={S}, M sharded over {world} GPUs" if args.shard_m
+                                else f"lutgemm fwd+bwd {bits}-bit M=K=N={S} per GPU"), "bits": bits, "M_per_gpu": M, "K": K,
                    "N": N, "parallelism": f"dp{world} (M sharded, NCCL all-reduce of grad_w)" if world > 1 else "single GPU",
                    "l2": f"{nsets} rotating input/output sets; a step touches {(h2d + d2h) / 2**20:.0f} MiB > L2"},
         "roofline": roofline, "cpu_baseline": cpu,
@@ -528,6 +532,8 @@ def main():
     ap.add_argument("--workload", choices=["lutgemm", "resnet18", "resnet50", "vit_s"], default="lutgemm")
     ap.add_argument("--batch", type=int, default=None, help="per-GPU batch of the model workloads")
     ap.add_argument("--conv-impl", choices=["layer", "fused", "unfold"], default="layer")
+    ap.add_argument("--shard-m", action="store_true",
+                    help="lutgemm workload: cut the M rows of ONE size^3 problem across the ranks (strong scaling)")
     ap.add_argument("--ste", action="store_true", help="model workloads: straight-through backward instead of the gradient tables")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
