@@ -12,8 +12,8 @@
 // The use-phase read is warp-uniform in x and contiguous in n: one 32-bit shared load per lane returns
 // two adjacent uint16 entries (two columns), conflict-free by construction - 64 table look-ups per
 // shared-memory wavefront instead of ~11.  The build reads the table transposed and paired ([w][x],
-// codes x and x + 2^b/2 in one word) with conflict-free 32-bit loads and writes slab rows (stride 33
-// words) with conflict-free 32-bit stores: 2^b * 2 wavefronts per k against 512 for the use phase.
+// codes x and x + 2^b/2 in one word) with conflict-free 32-bit loads and writes slab rows (stride 34
+// words) with conflict-free 64-bit stores: 2^b * 2 wavefronts per k against 512 for the use phase.
 // Two slab buffers: slab k+1 is built while slab k is read, one CTA barrier per k.
 // The two halves of a slab word go to the accumulators as  S += word,  H += word >> 16 ; at the end
 // sum(lo) = S - (H << 16) (mod 2^32) and sum(hi) = H.
@@ -40,7 +40,7 @@ struct Cfg {
     static constexpr int RT = 512;              // rows per CTA tile: 32 per warp
     static constexpr int CT = 64;               // columns per CTA tile: 2 per lane
     static constexpr int KC = 16;               // k per operand stage
-    static constexpr int U_STRIDE = 33;         // words per slab row (32 + 1 pad)
+    static constexpr int U_STRIDE = 34;         // words per slab row (32 + 2 pad: 8-byte aligned rows)
     static constexpr int TT_BYTES = Q * TT_STRIDE * 4;
     static constexpr int U_BYTES = Q * U_STRIDE * 4;
     static constexpr int RC_STAGE = KC * RT;
@@ -62,7 +62,9 @@ struct Args {
     int at_pitch;       // a multiple of 16; columns m >= M hold 0
 };
 
-template <int BITS>
+// USE_AT: the activation codes come from the transposed workspace copy (p.at); the other instantiation keeps
+// the direct / implicit-im2col fetch, so neither carries the other's registers.
+template <int BITS, bool USE_AT>
 __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p) {
     using C = Cfg<BITS>;
     constexpr int Q = C::Q, HALF = C::HALF, TTS = C::TT_STRIDE, RT = C::RT, CT = C::CT, KC = C::KC;
@@ -99,7 +101,7 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p) {
     auto fetch_chunk = [&](int m0, int n0, int chunk) {
         const int kbase = chunk * KC;
         const int m = min(m0 + tid, M - 1);
-        if (p.at) {
+        if (USE_AT) {
             // 16 rows of one k per thread, coalesced (instead of 16 k of one row, gathered for a convolution)
             const int gk = kbase + tid / (RT / 16), gm = m0 + (tid % (RT / 16)) * 16;
             prc = (gk < K && gm < p.at_pitch) ? *reinterpret_cast<const uint4 *>(p.at + (size_t)gk * p.at_pitch + gm)
@@ -119,7 +121,7 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p) {
         // codes are masked to BITS bits here, once, so no stray code can index outside a slab or the table
         const uint32_t tr[4] = {prc.x & MASK4, prc.y & MASK4, prc.z & MASK4, prc.w & MASK4};
         uint8_t *rs = rc_s + stage * C::RC_STAGE;
-        if (p.at) {
+        if (USE_AT) {
             *reinterpret_cast<uint4 *>(rs + (tid / (RT / 16)) * RT + (tid % (RT / 16)) * 16) =
                 make_uint4(tr[0], tr[1], tr[2], tr[3]);
         } else {
@@ -133,22 +135,21 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p) {
     // build slab `buf` for the k that sits at (stage, kk): warp wp fills column pairs 2wp and 2wp+1
     auto build = [&](int buf, int stage, int kk) {
         const uint32_t cw = *reinterpret_cast<const uint32_t *>(cc_s + stage * C::CC_STAGE + kk * CT + wp * 4);
-        const uint32_t ub = u_addr + buf * C::U_BYTES;
+        const uint32_t ub = u_addr + buf * C::U_BYTES + wp * 8;  // this warp's four columns: words 2wp and 2wp+1
+        const uint32_t y0 = byte_of(cw, 0), y1 = byte_of(cw, 1), y2 = byte_of(cw, 2), y3 = byte_of(cw, 3);
 #pragma unroll
-        for (int pp = 0; pp < 2; ++pp) {
-            const uint32_t y0 = byte_of(cw, 2 * pp), y1 = byte_of(cw, 2 * pp + 1);
-            const int pc = 2 * wp + pp;
-#pragma unroll
-            for (int j = 0; j < NSETS; ++j) {
-                const int i = lane + 32 * j;
-                if (HALF >= 32 || i < HALF) {
-                    const uint32_t r0 = lds_u32(tt_addr + (y0 * TTS + i) * 4);
-                    const uint32_t r1 = lds_u32(tt_addr + (y1 * TTS + i) * 4);
-                    const uint32_t lo = __byte_perm(r0, r1, 0x5410);  // { LUT[i][y0], LUT[i][y1] }
-                    const uint32_t hi = __byte_perm(r0, r1, 0x7632);  // { LUT[i+HALF][y0], LUT[i+HALF][y1] }
-                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(ub + (i * US + pc) * 4), "r"(lo) : "memory");
-                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(ub + ((i + HALF) * US + pc) * 4), "r"(hi) : "memory");
-                }
+        for (int j = 0; j < NSETS; ++j) {
+            const int i = lane + 32 * j;
+            if (HALF >= 32 || i < HALF) {
+                const uint32_t r0 = lds_u32(tt_addr + (y0 * TTS + i) * 4);
+                const uint32_t r1 = lds_u32(tt_addr + (y1 * TTS + i) * 4);
+                const uint32_t r2 = lds_u32(tt_addr + (y2 * TTS + i) * 4);
+                const uint32_t r3 = lds_u32(tt_addr + (y3 * TTS + i) * 4);
+                // { LUT[i][y0], LUT[i][y1] }, { LUT[i][y2], LUT[i][y3] } and the same for code i + HALF
+                asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(ub + i * (US * 4)), "r"(__byte_perm(r0, r1, 0x5410)),
+                             "r"(__byte_perm(r2, r3, 0x5410)) : "memory");
+                asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(ub + (i + HALF) * (US * 4)),
+                             "r"(__byte_perm(r0, r1, 0x7632)), "r"(__byte_perm(r2, r3, 0x7632)) : "memory");
             }
         }
     };
@@ -221,7 +222,7 @@ template <int BITS>
 static int launch_fwd_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int M, int K, int N,
                            const ConvGeom &conv, const uint8_t *at, int at_pitch, int num_sms, cudaStream_t stream) {
     using C = sf::Cfg<BITS>;
-    auto kern = sf::slab_fwd_kernel<BITS>;
+    auto kern = at ? sf::slab_fwd_kernel<BITS, true> : sf::slab_fwd_kernel<BITS, false>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
         return LUTGEMM_E_CUDA;
     sf::Args p{};
