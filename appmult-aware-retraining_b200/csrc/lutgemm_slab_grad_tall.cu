@@ -66,7 +66,9 @@ struct Args {
     int at_pitch;       // a multiple of 16; columns m >= M hold 0
 };
 
-template <int BITS, int MODE, int PF>
+// USE_AT (grad_w only): the row codes come from the transposed copy p.at; the other instantiation keeps the
+// direct / implicit-im2col fetch, so neither carries the other's registers.
+template <int BITS, int MODE, int PF, bool USE_AT>
 __global__ void __launch_bounds__(512, 1) slab_grad_tall_kernel(const Args p) {
     using C = Cfg<BITS>;
     constexpr int RW = C::RW, WARPS = C::WARPS;
@@ -134,7 +136,7 @@ __global__ void __launch_bounds__(512, 1) slab_grad_tall_kernel(const Args p) {
     };
     auto fetch_group = [&](int r0, int c0, int group) {
         const int kbase = group * KC;
-        if (MODE == kGw && p.at) {
+        if (MODE == kGw && USE_AT) {
             // row codes from the transposed copy at[k][m]: 16 rows per load, coalesced like the w operand
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
@@ -162,7 +164,7 @@ __global__ void __launch_bounds__(512, 1) slab_grad_tall_kernel(const Args p) {
         uint8_t *rs = rc_s + stage * C::RC_STAGE;
         uint8_t *cs = cc_s + stage * C::CC_STAGE;
         const uint32_t tc[4] = {pcc.x & MASK4, pcc.y & MASK4, pcc.z & MASK4, pcc.w & MASK4};
-        if (MODE == kGw && p.at) {
+        if (MODE == kGw && USE_AT) {
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 const int idx = tid + THREADS * j, kq = idx / (RT / 16);
@@ -355,7 +357,9 @@ static int launch_slab_grad_tall(const float *gc, const uint8_t *a, const uint8_
     using C = sgt::Cfg<BITS>;
     static_assert(C::RT == kSlabTallRows, "tile height");
     static_assert(C::SMEM <= 232448, "shared memory budget");
-    auto kern = sgt::slab_grad_tall_kernel<BITS, MODE, 4>;
+    const bool use_at = MODE == sgt::kGw && at != nullptr;
+    auto kern = use_at ? sgt::slab_grad_tall_kernel<BITS, MODE, 4, MODE == sgt::kGw>
+                       : sgt::slab_grad_tall_kernel<BITS, MODE, 4, false>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
         return LUTGEMM_E_CUDA;
     const int RDIM = MODE == sgt::kGa ? N : M, CDIM = MODE == sgt::kGa ? M : N;
