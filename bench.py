@@ -373,7 +373,7 @@ def run_ours(args, rank, world, local_rank):
                 "frac": alg_bytes[dom] / (kern_ms[dom] * 1e-3) / 1e9 / peaks["hbm_gbs"], "of": peaks_kind},
         # dram__bytes_read.sum + dram__bytes_write.sum per launch of that kernel from the ncu capture
         # summarised in profiles/slab_kernels_b8_4096.md (only that configuration was captured)
-        "traffic": ({"forward": 117.7e6, "grad_w": 360.9e6, "grad_a": 359.2e6}[names[dom]]
+        "traffic": ({"forward": 118.0e6, "grad_w": 360.8e6, "grad_a": 358.3e6}[names[dom]]
                     if (bits, S, M) == (8, 4096, 4096) else None),
         "traffic_unit": "bytes per launch (ncu, 8-bit 4096^3)",
     }
