@@ -48,3 +48,28 @@ def test_signed_tables_follow_the_sign_magnitude_definition():
         assert fp_s[ca, cw] - offset == sa * sw * fp[a, w]
         assert ga_s[ca, cw] == sw * round(ga[a, w] * 16)
         assert gb_s[ca, cw] == sa * round(gb[a, w] * 16)
+
+
+def test_config0_on_the_cpu_oracle():
+    """Benchmark configuration 0 (7-bit magnitudes with sign bits, M=256, K=512, N=256) evaluated on the CPU: the
+    signed tables through the C oracle's 8-bit unsigned forward equal the direct signed sum."""
+    from lutgemm_signed import signed_dense_tables
+    from oracle.oracle_c import OracleC
+    bits, M, K, N = 7, 256, 512, 256
+    q = 1 << bits
+    fp, ga, gb = O.synthetic_tables(bits, seed=0, half_window=8)
+    fp_s, ga_s, gb_s, offset = signed_dense_tables(fp, ga, gb)
+    rng = np.random.default_rng(0)
+    a_mag, w_mag = rng.integers(0, q, (M, K)), rng.integers(0, q, (K, N))
+    a_neg, w_neg = rng.random((M, K)) < 0.5, rng.random((K, N)) < 0.5
+    a_codes = (a_mag | (a_neg.astype(np.int64) << bits)).astype(np.uint8)
+    w_codes = (w_mag | (w_neg.astype(np.int64) << bits)).astype(np.uint8)
+    lf = O.pack_padded(fp_s, bits + 1, np.uint16)
+    c = OracleC().forward(a_codes, w_codes, lf, bits + 1).astype(np.int64) - K * offset
+    sa, sw = np.where(a_neg, -1, 1).astype(np.int64), np.where(w_neg, -1, 1).astype(np.int64)
+    want = np.zeros((M, N), np.int64)
+    for k in range(K):
+        want += (sa[:, k, None] * sw[None, k, :]) * fp[a_mag[:, k, None], w_mag[None, k, :]]
+    assert np.array_equal(c, want)
+    out = c * (0.05 * 0.01)  # the configuration's activation and weight scales
+    assert np.isfinite(out).all()
