@@ -37,7 +37,7 @@ struct GaCfg {
 };
 
 template <int BITS, int R, int C, int WM, int WK>
-__global__ void __launch_bounds__(32 * WM * WK, WM * WK <= 8 ? 2 : 1)
+__global__ void __launch_bounds__(32 * WM * WK, WM * WK <= 8 ? (C <= 2 ? 4 : 2) : 1)
 ga_colbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, const uint8_t *__restrict__ w,
                    float *__restrict__ ga, const int16_t *__restrict__ lut, int M, int K, int N, int tiles_m,
                    int tiles_k, int vec_g, int vec_w, int vec_o, const ConvGeom conv) {
@@ -193,7 +193,10 @@ static int launch_ga(const float *gc, const uint8_t *a, const uint8_t *w, float 
         return LUTGEMM_E_CUDA;
     const int tiles_m = (M + Cfg::MT - 1) / Cfg::MT, tiles_k = (K + Cfg::KT - 1) / Cfg::KT;
     const long tiles = (long)tiles_m * tiles_k;
-    const int ctas_per_sm = Cfg::SMEM <= 100 * 1024 ? 2 : 1;
+    int ctas_per_sm = 1;  // persistent grid: as many CTAs as the SMs hold at once
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, kern, Cfg::THREADS, Cfg::SMEM) != cudaSuccess ||
+        ctas_per_sm < 1)
+        ctas_per_sm = 1;
     const int grid = (int)(tiles < (long)num_sms * ctas_per_sm ? tiles : (long)num_sms * ctas_per_sm);
     const int vec_g = (N % 4 == 0) && ((reinterpret_cast<uintptr_t>(gc) & 15) == 0);
     const int vec_w = (N % 16 == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
@@ -208,6 +211,8 @@ int backward_ga(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, 
     switch (bits) {
         case 4: return launch_ga<4, 8, 4, 2, 4>(gc, a, w, ga, lut_ga, M, K, N, conv, num_sms, stream);
         case 6: return launch_ga<6, 8, 4, 2, 4>(gc, a, w, ga, lut_ga, M, K, N, conv, num_sms, stream);
+        // (two columns per thread and four CTAs per SM instead of four and two measured 1-3 % slower: the kernel
+        // is bound by the bank conflicts of its gather, not by latency)
         case 7: return launch_ga<7, 8, 4, 2, 4>(gc, a, w, ga, lut_ga, M, K, N, conv, num_sms, stream);
         // the 128 KB table leaves room for one CTA per SM only: make it 16 warps
         case 8: return launch_ga<8, 8, 4, 4, 4>(gc, a, w, ga, lut_ga, M, K, N, conv, num_sms, stream);
