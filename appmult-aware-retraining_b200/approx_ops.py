@@ -60,6 +60,8 @@ def _load():
     lib.lutgemm_backward_scratch_bytes.argtypes = [ci, ci, ci, ci]
     lib.lutgemm_backward.restype = ci
     lib.lutgemm_backward.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp, sz, vp]
+    lib.lutgemm_backward_ws.restype = ci
+    lib.lutgemm_backward_ws.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp, vp, sz, vp]
     lib.lutgemm_conv2d_forward.restype = ci
     lib.lutgemm_conv2d_forward.argtypes = [vp, vp, vp, vp] + [ci] * 11 + [vp]
     lib.lutgemm_conv2d_backward_scratch_bytes.restype = sz
@@ -123,8 +125,11 @@ def _stream_ptr(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
-def approx_gemm_forward(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, lut: torch.Tensor) -> None:
-    """c[m,n] = sum_k lut[a[m,k]*(2^bits+2) + b[k,n]], written in place into the uint32 tensor c."""
+def approx_gemm_forward(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, lut: torch.Tensor):
+    """c[m,n] = sum_k lut[a[m,k]*(2^bits+2) + b[k,n]], written in place into the uint32 tensor c.
+    Returns the transposed activation codes the kernel worked from (a uint8 tensor that
+    `approx_gemm_backward(..., codes_t=...)` of the same `a` can reuse), or None; callers of the reference
+    signature simply ignore it."""
     _check_input(a, torch.uint8, "a_tensor")
     _check_input(b, torch.uint8, "b_tensor")
     _check_input(c, torch.uint32, "c_tensor")
@@ -154,10 +159,11 @@ def approx_gemm_forward(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, lut: 
         rc = lib.lutgemm_forward_ws(a.data_ptr(), b.data_ptr(), c.data_ptr(), lut.data_ptr(), bits, M, K, N,
                                     scratch.data_ptr() if nbytes else None, nbytes, _stream_ptr(dev))
     _check(rc, "approx_gemm_forward")
+    return scratch
 
 
 def approx_gemm_backward(gc: torch.Tensor, a: torch.Tensor, b: torch.Tensor, ga: torch.Tensor, gb: torch.Tensor,
-                         lut_grad_a: torch.Tensor, lut_grad_b: torch.Tensor) -> None:
+                         lut_grad_a: torch.Tensor, lut_grad_b: torch.Tensor, codes_t: torch.Tensor = None) -> None:
     """ga = 1/16 * sum_n gc * LUTa[a][b],  gb = 1/16 * sum_m LUTb[a][b] * gc, written in place."""
     _check_input(gc, torch.float32, "gc_tensor")
     _check_input(a, torch.uint8, "a_tensor")
@@ -193,9 +199,14 @@ def approx_gemm_backward(gc: torch.Tensor, a: torch.Tensor, b: torch.Tensor, ga:
     with torch.cuda.device(dev):
         nbytes = lib.lutgemm_backward_scratch_bytes(bits, M, K, N)
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev) if nbytes else None
-        rc = lib.lutgemm_backward(gc.data_ptr(), a.data_ptr(), b.data_ptr(), ga.data_ptr(), gb.data_ptr(),
-                                  lut_grad_a.data_ptr(), lut_grad_b.data_ptr(), bits, M, K, N,
-                                  scratch.data_ptr() if scratch is not None else None, nbytes, _stream_ptr(dev))
+        if codes_t is not None:
+            _check_input(codes_t, torch.uint8, "codes_t")
+            if codes_t.numel() != K * ((M + 15) // 16 * 16):
+                raise RuntimeError("codes_t does not belong to this a_tensor")
+        rc = lib.lutgemm_backward_ws(gc.data_ptr(), a.data_ptr(), b.data_ptr(), ga.data_ptr(), gb.data_ptr(),
+                                     lut_grad_a.data_ptr(), lut_grad_b.data_ptr(), bits, M, K, N,
+                                     codes_t.data_ptr() if codes_t is not None else None,
+                                     scratch.data_ptr() if scratch is not None else None, nbytes, _stream_ptr(dev))
     _check(rc, "approx_gemm_backward")
 
 

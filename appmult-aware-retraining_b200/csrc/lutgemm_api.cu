@@ -256,6 +256,14 @@ int lutgemm_backward(const float *gc, const uint8_t *a, const uint8_t *w, float 
     return backward_impl(gc, a, w, ga, gw, lut_ga, lut_gw, bits, M, K, N, none, nullptr, scratch, scratch_bytes, stream);
 }
 
+int lutgemm_backward_ws(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, float *gw,
+                        const int16_t *lut_ga, const int16_t *lut_gw, int bits, int M, int K, int N,
+                        const uint8_t *codes_t, void *scratch, size_t scratch_bytes, void *stream) {
+    if (reinterpret_cast<uintptr_t>(codes_t) & 15) return LUTGEMM_E_BADARG;
+    lutgemm::ConvGeom none{};
+    return backward_impl(gc, a, w, ga, gw, lut_ga, lut_gw, bits, M, K, N, none, codes_t, scratch, scratch_bytes, stream);
+}
+
 // ---- convolution entry points (implicit im2col) ------------------------------------------------------------
 static int make_geom(int B, int C, int H, int W, int kh, int kw, int stride, int pad, int dil, lutgemm::ConvGeom *g) {
     if (B <= 0 || C <= 0 || H <= 0 || W <= 0 || kh <= 0 || kw <= 0 || stride <= 0 || pad < 0 || dil <= 0)

@@ -166,12 +166,13 @@ class _AppLinearLayer(torch.autograd.Function):
         qw = torch.clamp(torch.round(weight / s_w - z_w), 0.0, w_qmax)
         wmat = qw.t().to(torch.uint8).contiguous()
         y = torch.empty((M, N), dtype=torch.uint32, device=x2.device)
-        approx_ops.approx_gemm_forward(codes, wmat, y, _ops_state.lut_appmult)
+        codes_t = approx_ops.approx_gemm_forward(codes, wmat, y, _ops_state.lut_appmult)
         box = codes.sum(dim=1, dtype=torch.float32)
         sumw_t = qw.sum(dim=1).view(1, N).contiguous()
         taps = torch.full((1,), float(K), device=x2.device)
         out = approx_ops.conv2d_epilogue(y, box, sumw_t, taps, s_a, s_w, z_a, z_w, bias, 1)
         ctx.save_for_backward(x2, codes, wmat, weight, quant)
+        ctx.codes_t = codes_t  # transposed codes of the forward kernel: the grad_w kernel reuses them
         ctx.cfg = (a_qmax, w_qmax, bias is not None)
         return out
 
@@ -185,7 +186,9 @@ class _AppLinearLayer(torch.autograd.Function):
         need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         ga = torch.empty((M, K), dtype=torch.float32, device=gy.device)
         gw = torch.empty(wmat.shape, dtype=torch.float32, device=gy.device)
-        approx_ops.approx_gemm_backward(gy, codes, wmat, ga, gw, _ops_state.lut_grad_a, _ops_state.lut_grad_b)
+        approx_ops.approx_gemm_backward(gy, codes, wmat, ga, gw, _ops_state.lut_grad_a, _ops_state.lut_grad_b,
+                                        codes_t=ctx.codes_t)
+        ctx.codes_t = None
         gx = gwt = gb = None
         if need_x:
             ga.add_(z_w * gy.sum(dim=1, keepdim=True))  # cross term z_w * rowsum(q_a)

@@ -223,7 +223,8 @@ def run_ours(args, rank, world, local_rank):
     fwd_ws_bytes = lib.lutgemm_forward_scratch_bytes(bits, M, K, N)  # transposed activation codes
     fwd_ws = torch.empty(max(1, fwd_ws_bytes), dtype=torch.uint8, device=dev)
     # + the code transposition and the two block-reduce kernels of the slab path, or the split-M reduce kernel
-    launches_per_step = 3 + ((3 if bits >= 7 else 1) if scratch_bytes else 0) + (1 if fwd_ws_bytes else 0)
+    # (the transposition runs once per step: the grad_w kernel reuses the forward pass's copy)
+    launches_per_step = 3 + ((2 if bits >= 7 else 1) if scratch_bytes else 0) + (1 if fwd_ws_bytes else 0)
     stream = torch.cuda.current_stream(dev)
 
     def fwd(s):
@@ -232,8 +233,10 @@ def run_ours(args, rank, world, local_rank):
         assert rc == 0, lib.lutgemm_status_string(rc)
 
     def bwd_gw(s):
-        rc = lib.lutgemm_backward(s["gc"].data_ptr(), s["a"].data_ptr(), s["w"].data_ptr(), None, s["gw"].data_ptr(),
-                                  None, lw.data_ptr(), bits, M, K, N, scratch.data_ptr(), scratch_bytes, stream.cuda_stream)
+        # the forward pass of the same step left the transposed activation codes in its workspace
+        rc = lib.lutgemm_backward_ws(s["gc"].data_ptr(), s["a"].data_ptr(), s["w"].data_ptr(), None, s["gw"].data_ptr(),
+                                     None, lw.data_ptr(), bits, M, K, N, fwd_ws.data_ptr() if fwd_ws_bytes else None,
+                                     scratch.data_ptr(), scratch_bytes, stream.cuda_stream)
         assert rc == 0, lib.lutgemm_status_string(rc)
 
     def bwd_ga(s):

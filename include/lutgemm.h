@@ -91,6 +91,15 @@ int lutgemm_backward(const float *gc, const uint8_t *a, const uint8_t *w, float 
                      void *scratch, size_t scratch_bytes, void *stream);
 
 /*
+ * lutgemm_backward with the transposed activation codes that lutgemm_forward_ws left in its workspace for the
+ * same `a` (codes_t, [K][M rounded up to 16] uint8; may be NULL): the weight-gradient kernel then skips its own
+ * transposition.  Same results.  No counterpart in the reference.
+ */
+int lutgemm_backward_ws(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, float *gw,
+                        const int16_t *lut_ga, const int16_t *lut_gw, int bits, int M, int K, int N,
+                        const uint8_t *codes_t, void *scratch, size_t scratch_bytes, void *stream);
+
+/*
  * Convolution forward with the im2col fused into the operand loader (no unfolded tensor in HBM):
  *   y[(b*Ho+oh)*Wo+ow, n] = sum_{c,i,j} lut[ x[b,c,oh*stride-pad+i*dil,ow*stride-pad+j*dil] * (2^bits+2) + wmat[(c*kh+i)*kw+j, n] ]
  * with code 0 outside the image (spatial padding looks up lut[0][w], as in the reference).

@@ -384,6 +384,14 @@ def test_workspace_entry_points_match_the_plain_ones(dev, bits):
         assert torch.equal(ws.view(K, -1)[:, :M], at.t())            # the workspace holds the transposed codes
         assert lib.lutgemm_forward_ws(at.data_ptr(), wt.data_ptr(), c1.data_ptr(), lf.data_ptr(), bits, M, K, N,
                                       ws.data_ptr(), nbytes - 1, stream) == -4   # LUTGEMM_E_SCRATCH
+        # the GEMM backward fed the forward pass's transposed codes gives the same gradients as one making its own
+        gct = torch.randn(M, N, device=dev)
+        res = []
+        for given in (None, ws):
+            ga_, gw_ = torch.empty(M, K, device=dev), torch.empty(K, N, device=dev)
+            approx_ops.approx_gemm_backward(gct, at, wt, ga_, gw_, la, lw, codes_t=given)
+            res.append((ga_, gw_))
+        assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
     B, Cin, H, W, Cout, k, st, p = 3, 16, 32, 32, 64, 3, 1, 1
     rng = np.random.default_rng(7 + bits)
     x = torch.from_numpy(rng.integers(0, 1 << bits, (B, Cin, H, W)).astype(np.uint8)).to(dev)
