@@ -128,6 +128,11 @@ def cpu_port_rate(bits, K, N, lf, la, lw, w, target_seconds=12.0, rows_cap=4096,
     same problem (same K, N and weight codes; `rows` activation rows)."""
     from oracle import OracleC
     oc = OracleC()
+    # all the host threads this process may use: launchers such as torchrun export OMP_NUM_THREADS=1
+    try:
+        oc.set_num_threads(len(os.sched_getaffinity(0)))
+    except AttributeError:
+        oc.set_num_threads(os.cpu_count() or 1)
     rng = np.random.default_rng(seed)
     q = 1 << bits
 
