@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p) {
             const uint32_t ub = u_addr + (k & 1) * C::U_BYTES + lane * 4;
 #pragma unroll
             for (int r = 0; r < 32; ++r) {
-                // slab row address = base + 132 * code in one integer dot-product instruction
+                // slab row address = base + 136 * code in one integer dot-product instruction
                 const uint32_t addr = byte_scaled_add<US * 4>(rv[r >> 2], r & 3, ub);
                 uint32_t word;
                 asm volatile("ld.shared.u32 %0, [%1];" : "=r"(word) : "r"(addr));
