@@ -75,6 +75,10 @@ def _load():
     lib.lutgemm_quantize_activations_backward.argtypes = [vp, cl, cl, cl, cl, ci, ci, ci, ci, vp, vp, cf, vp, vp, vp, vp, vp, vp]
     lib.lutgemm_conv2d_epilogue.restype = ci
     lib.lutgemm_conv2d_epilogue.argtypes = [vp] * 10 + [cl, ci, ci, vp]
+    lib.lutgemm_kernel_launches.restype = ctypes.c_ulonglong
+    lib.lutgemm_kernel_launches.argtypes = []
+    lib.lutgemm_set_kernel_choice.restype = ci
+    lib.lutgemm_set_kernel_choice.argtypes = [ci, ci, ci]
     lib.lutgemm_device_error.restype = ci
     lib.lutgemm_device_error.argtypes = [ctypes.POINTER(ci)]
     lib.lutgemm_selftest_bounded_wait.restype = ci
@@ -86,6 +90,18 @@ def _load():
 def library():
     """The loaded ctypes handle of liblutgemm_b200.so (raises if it has not been built)."""
     return _load()
+
+
+_FORWARD_CHOICES = {"auto": 0, "rowbcast": 1, "slab": 2}
+_BACKWARD_CHOICES = {"auto": 0, "bcast": 1, "slab": 2}
+_TILE_CHOICES = {"auto": 0, "wide": 1, "tall": 2}
+
+
+def set_kernel_choice(forward: str = "auto", backward: str = "auto", grad_tile: str = "auto") -> None:
+    """Process-wide kernel-family override (tests, A/B timing); all "auto" restores the choice by shape.
+    forward: "rowbcast" | "slab"; backward: "bcast" | "slab"; grad_tile: "wide" (512 x 64) | "tall" (1024 x 32)."""
+    _check(_load().lutgemm_set_kernel_choice(_FORWARD_CHOICES[forward], _BACKWARD_CHOICES[backward],
+                                             _TILE_CHOICES[grad_tile]), "set_kernel_choice")
 
 
 def device_error() -> int:

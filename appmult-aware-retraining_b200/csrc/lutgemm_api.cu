@@ -4,6 +4,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <atomic>
+
 #include "lutgemm.h"
 #include "lutgemm_common.cuh"
 #include "lutgemm_kernels.h"
@@ -15,10 +17,10 @@ int g_num_sms[kMaxDevices];  // 0 = not queried yet; written with the same value
 
 int current_num_sms() {
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+    if (!lutgemm::cuda_ok(cudaGetDevice(&dev))) return -1;
     if (dev >= 0 && dev < kMaxDevices && g_num_sms[dev] > 0) return g_num_sms[dev];
     int sms = 0;
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return -1;
+    if (!lutgemm::cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) || sms <= 0) return -1;
     if (dev >= 0 && dev < kMaxDevices) g_num_sms[dev] = sms;
     return sms;
 }
@@ -37,10 +39,14 @@ double tall_fill(long rows, long cols) {
     return (double)rows * (double)cols / ((double)tr * 1024.0 * (double)tc * 32.0);
 }
 
-bool env_is(const char *name, const char *value) {
-    const char *e = getenv(name);
-    return e && !strcmp(e, value);
-}
+// kernel-family overrides set through lutgemm_set_kernel_choice (0 = automatic choice by shape)
+std::atomic<int> g_force_forward{0}, g_force_backward{0}, g_force_tile{0};
+
+// the CUDA error behind the calling thread's last LUTGEMM_E_CUDA (launchers clear the runtime's own record)
+thread_local cudaError_t g_last_cuda_error = cudaSuccess;
+
+// kernels launched by this library in this process (every launch site reports through launch_status)
+std::atomic<unsigned long long> g_kernel_launches{0};
 
 struct BackwardPlan {
     bool gw_slab, ga_slab;
@@ -57,7 +63,7 @@ struct BackwardPlan {
 // Kernel choice for the two gradients.  Slab kernels amortise one slab build over 512 rows of the
 // reduction dimension (M for grad_w, N for grad_a), so they need that dimension long and the tiles
 // reasonably full; everything else goes to the row/column-broadcast kernels.
-// LUTGEMM_BACKWARD_KERNEL=bcast|slab overrides (for A/B timing).
+// lutgemm_set_kernel_choice overrides the choice (tests, A/B timing).
 BackwardPlan plan_backward(int bits, int M, int K, int N, int sms) {
     BackwardPlan pl{};
     // measured on B200 at 4096^3 (ms, grad_w / grad_a): tall fp32-slab 15.9 / 16.4 (8 bit), 14.1 / 14.4 (7 bit)
@@ -70,12 +76,13 @@ BackwardPlan plan_backward(int bits, int M, int K, int N, int sms) {
     // roofline at 7 bits and 29 % at 8 bits whatever N is, when the better of the two tilings is this full)
     const double ga_fill = slab_fill(N, M) > tall_fill(N, M) ? slab_fill(N, M) : tall_fill(N, M);
     pl.ga_slab = bits >= 7 && N >= 768 && M >= 32 && ga_fill >= (bits == 7 ? 0.85 : 0.7);
-    if (env_is("LUTGEMM_BACKWARD_KERNEL", "bcast")) pl.gw_slab = pl.ga_slab = false;
-    if (env_is("LUTGEMM_BACKWARD_KERNEL", "slab")) pl.gw_slab = pl.ga_slab = true;
+    const int force = g_force_backward.load(std::memory_order_relaxed), tile = g_force_tile.load(std::memory_order_relaxed);
+    if (force == LUTGEMM_BACKWARD_BCAST) pl.gw_slab = pl.ga_slab = false;
+    if (force == LUTGEMM_BACKWARD_SLAB) pl.gw_slab = pl.ga_slab = true;
     pl.gw_tall = pl.gw_slab && tall_fill(M, N) >= 0.85 * slab_fill(M, N);
     pl.ga_tall = pl.ga_slab && tall_fill(N, M) >= 0.85 * slab_fill(N, M);
-    if (env_is("LUTGEMM_GRAD_TILE", "wide")) pl.gw_tall = pl.ga_tall = false;
-    if (env_is("LUTGEMM_GRAD_TILE", "tall")) { pl.gw_tall = pl.gw_slab; pl.ga_tall = pl.ga_slab; }
+    if (tile == LUTGEMM_TILE_WIDE) pl.gw_tall = pl.ga_tall = false;
+    if (tile == LUTGEMM_TILE_TALL) { pl.gw_tall = pl.gw_slab; pl.ga_tall = pl.ga_slab; }
     pl.gw_splits = pl.gw_slab ? 1 : lutgemm::gw_num_splits(bits, M, K, N, sms);
     if (pl.gw_slab) {
         const int rb = pl.gw_tall ? lutgemm::slab_tall_row_blocks(M) : lutgemm::slab_f32_row_blocks(M);
@@ -95,9 +102,23 @@ BackwardPlan plan_backward(int bits, int M, int K, int N, int sms) {
 
 }  // namespace
 
+namespace lutgemm {
+
+void record_cuda_error(cudaError_t e) { g_last_cuda_error = e; }
+
+int launch_status() {
+    g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+    const cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) return LUTGEMM_OK;
+    g_last_cuda_error = e;
+    return LUTGEMM_E_CUDA;
+}
+
+}  // namespace lutgemm
+
 extern "C" {
 
-int lutgemm_version(void) { return 100; }
+int lutgemm_version(void) { return 200; }
 
 const char *lutgemm_status_string(int status) {
     switch (status) {
@@ -107,12 +128,22 @@ const char *lutgemm_status_string(int status) {
         case LUTGEMM_E_SCRATCH: return "scratch buffer too small";
         case LUTGEMM_E_TOOLARGE: return "problem size beyond what this entry point supports";
         case LUTGEMM_E_CUDA: {
-            cudaError_t e = cudaPeekAtLastError();
-            snprintf(g_msg, sizeof(g_msg), "CUDA failure: %s", cudaGetErrorString(e));
+            snprintf(g_msg, sizeof(g_msg), "CUDA failure: %s", cudaGetErrorString(g_last_cuda_error));
             return g_msg;
         }
     }
     return "unknown status";
+}
+
+unsigned long long lutgemm_kernel_launches(void) { return g_kernel_launches.load(std::memory_order_relaxed); }
+
+int lutgemm_set_kernel_choice(int forward, int backward, int grad_tile) {
+    if (forward < 0 || forward > 2 || backward < 0 || backward > 2 || grad_tile < 0 || grad_tile > 2)
+        return LUTGEMM_E_BADARG;
+    g_force_forward.store(forward, std::memory_order_relaxed);
+    g_force_backward.store(backward, std::memory_order_relaxed);
+    g_force_tile.store(grad_tile, std::memory_order_relaxed);
+    return LUTGEMM_OK;
 }
 
 int lutgemm_lut_elem_num(int bits) {
@@ -129,11 +160,12 @@ int lutgemm_bits_from_elem_num(long elem_num) {
 
 // ---- shared bodies of the GEMM and the implicit-im2col entry points ------------------------------------
 // Large-M problems with reasonably filled 512x64 tiles go to the slab kernel; small or skinny ones to the
-// row-broadcast kernel.  LUTGEMM_FORWARD_KERNEL=rowbcast|slab overrides (for A/B timing).
+// row-broadcast kernel.  lutgemm_set_kernel_choice overrides the choice (tests, A/B timing).
 static bool forward_uses_slab(int M, int N) {
     bool slab = M >= 512 && N >= 32 && slab_fill(M, N) >= 0.6;
-    if (env_is("LUTGEMM_FORWARD_KERNEL", "rowbcast")) slab = false;
-    if (env_is("LUTGEMM_FORWARD_KERNEL", "slab")) slab = true;
+    const int force = g_force_forward.load(std::memory_order_relaxed);
+    if (force == LUTGEMM_FORWARD_ROWBCAST) slab = false;
+    if (force == LUTGEMM_FORWARD_SLAB) slab = true;
     return slab;
 }
 
@@ -152,11 +184,6 @@ static int forward_impl(const uint8_t *a, const uint8_t *w, uint32_t *c, const u
     if (sms <= 0) return LUTGEMM_E_CUDA;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (forward_uses_slab(M, N)) {
-        // Two implementations of the slab algorithm: barrier-synchronous (default: faster on B200 at 7 and
-        // 8 bits, where four producer warps cannot build slabs fast enough) and warp-specialised
-        // (LUTGEMM_SLAB_IMPL=ws, plain GEMM operands only).
-        if (!conv.enabled && env_is("LUTGEMM_SLAB_IMPL", "ws"))
-            return lutgemm::forward_slab_ws(a, w, c, lut, bits, M, K, N, sms, s);
         const uint8_t *at = nullptr;
         const int pitch = codes_pitch(M);
         if (scratch) {
@@ -178,7 +205,7 @@ int lutgemm_forward(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint1
 
 size_t lutgemm_forward_scratch_bytes(int bits, int M, int K, int N) {
     if (!lutgemm::bits_supported(bits) || M <= 0 || K <= 0 || N <= 0) return 0;
-    if (!forward_uses_slab(M, N) || env_is("LUTGEMM_SLAB_IMPL", "ws")) return 0;
+    if (!forward_uses_slab(M, N)) return 0;
     return (size_t)codes_pitch(M) * K;
 }
 
@@ -190,11 +217,11 @@ int lutgemm_forward_ws(const uint8_t *a, const uint8_t *w, uint32_t *c, const ui
 
 int lutgemm_device_error(int *value) {
     if (!value) return LUTGEMM_E_BADARG;
-    return lutgemm::slab_ws_read_and_clear_error(value);
+    return lutgemm::read_and_clear_device_error(value);
 }
 
 int lutgemm_selftest_bounded_wait(void *stream) {
-    return lutgemm::slab_ws_bounded_wait_selftest(static_cast<cudaStream_t>(stream));
+    return lutgemm::bounded_wait_selftest(static_cast<cudaStream_t>(stream));
 }
 
 size_t lutgemm_backward_scratch_bytes(int bits, int M, int K, int N) {
@@ -221,19 +248,17 @@ static int backward_impl(const float *gc, const uint8_t *a, const uint8_t *w, fl
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const BackwardPlan pl = plan_backward(bits, M, K, N, sms);
     float *sc = static_cast<float *>(scratch);
-    const bool ws_impl = !conv.enabled && env_is("LUTGEMM_SLAB_IMPL", "ws");
     if (gw) {
         // the weight gradient goes first: under data parallelism its all-reduce can then overlap gA
         if (pl.gw_scratch && (!scratch || scratch_bytes < pl.gw_scratch)) return LUTGEMM_E_SCRATCH;
         const uint8_t *at = codes_t;  // left by the forward pass (same layout), or made here
-        if (pl.gw_slab && pl.gw_at_pitch && !ws_impl && !at) {
+        if (pl.gw_slab && pl.gw_at_pitch && !at) {
             uint8_t *dst = static_cast<uint8_t *>(scratch) + pl.gw_at_offset;
             const int trc = lutgemm::transpose_codes(a, dst, M, K, pl.gw_at_pitch, conv, s);
             if (trc != LUTGEMM_OK) return trc;
             at = dst;
         }
         int rc = !pl.gw_slab ? lutgemm::backward_gw(gc, a, w, gw, lut_gw, bits, M, K, N, conv, sc, pl.gw_splits, sms, s)
-                 : ws_impl   ? lutgemm::backward_gw_slab_ws(gc, a, w, gw, lut_gw, bits, M, K, N, sc, sms, s)
                  : pl.gw_tall ? lutgemm::backward_gw_slab_tall(gc, a, w, gw, lut_gw, bits, M, K, N, conv, sc, at, pl.gw_at_pitch, sms, s)
                              : lutgemm::backward_gw_slab_f32(gc, a, w, gw, lut_gw, bits, M, K, N, conv, sc, at, pl.gw_at_pitch, sms, s);
         if (rc != LUTGEMM_OK) return rc;
@@ -241,7 +266,6 @@ static int backward_impl(const float *gc, const uint8_t *a, const uint8_t *w, fl
     if (ga) {
         if (pl.ga_scratch && (!scratch || scratch_bytes < pl.ga_scratch)) return LUTGEMM_E_SCRATCH;
         int rc = !pl.ga_slab ? lutgemm::backward_ga(gc, a, w, ga, lut_ga, bits, M, K, N, conv, sms, s)
-                 : ws_impl   ? lutgemm::backward_ga_slab_ws(gc, a, w, ga, lut_ga, bits, M, K, N, sc, sms, s)
                  : pl.ga_tall ? lutgemm::backward_ga_slab_tall(gc, a, w, ga, lut_ga, bits, M, K, N, conv, sc, sms, s)
                              : lutgemm::backward_ga_slab_f32(gc, a, w, ga, lut_ga, bits, M, K, N, conv, sc, sms, s);
         if (rc != LUTGEMM_OK) return rc;
@@ -328,7 +352,7 @@ int lutgemm_conv2d_backward_ws(const float *gy, const uint8_t *x, const uint8_t 
     rc = backward_impl(gy, x, wmat, gx ? gcol : nullptr, gw, lut_ga, lut_gw, bits, M, K, Cout, g, codes_t, rest,
                        rest_bytes, stream);
     if (rc != LUTGEMM_OK) return rc;
-    if (gx) return lutgemm::col2im_gather(gcol, gx, g, static_cast<cudaStream_t>(stream));
+    if (gx) return lutgemm::col2im_gather(gcol, gx, g, current_num_sms(), static_cast<cudaStream_t>(stream));
     return LUTGEMM_OK;
 }
 

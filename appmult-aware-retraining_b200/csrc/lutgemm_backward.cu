@@ -189,7 +189,7 @@ static int launch_ga(const float *gc, const uint8_t *a, const uint8_t *w, float 
                      int K, int N, const ConvGeom &conv, int num_sms, cudaStream_t stream) {
     using Cfg = GaCfg<BITS, R, C, WM, WK>;
     auto kern = ga_colbcast_kernel<BITS, R, C, WM, WK>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess)
+    if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM)))
         return LUTGEMM_E_CUDA;
     const int tiles_m = (M + Cfg::MT - 1) / Cfg::MT, tiles_k = (K + Cfg::KT - 1) / Cfg::KT;
     const long tiles = (long)tiles_m * tiles_k;
@@ -203,7 +203,7 @@ static int launch_ga(const float *gc, const uint8_t *a, const uint8_t *w, float 
     const int vec_o = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(ga) & 15) == 0);
     kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(gc, a, w, ga, lut, M, K, N, tiles_m, tiles_k, vec_g, vec_w, vec_o,
                                                     conv);
-    return cudaGetLastError() == cudaSuccess ? LUTGEMM_OK : LUTGEMM_E_CUDA;
+    return launch_status();
 }
 
 int backward_ga(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, const int16_t *lut_ga, int bits,
@@ -406,7 +406,7 @@ static int launch_gw(const float *gc, const uint8_t *a, const uint8_t *w, float 
                      cudaStream_t stream) {
     using Cfg = GwCfg<BITS, R, C, WK, WN>;
     auto kern = gw_rowbcast_kernel<BITS, R, C, WK, WN>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess)
+    if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM)))
         return LUTGEMM_E_CUDA;
     const int tiles_k = (K + Cfg::KT - 1) / Cfg::KT, tiles_n = (N + Cfg::NT - 1) / Cfg::NT;
     const long items = (long)tiles_k * tiles_n * num_splits;
@@ -420,12 +420,12 @@ static int launch_gw(const float *gc, const uint8_t *a, const uint8_t *w, float 
     const float scale = num_splits > 1 ? 1.0f : kGradFactor;
     kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(gc, a, w, out, lut, M, K, N, tiles_k, tiles_n, num_splits,
                                                     rows_per_split, scale, vec_a, vec_g, conv);
-    if (cudaGetLastError() != cudaSuccess) return LUTGEMM_E_CUDA;
+    if (launch_status() != LUTGEMM_OK) return LUTGEMM_E_CUDA;
     if (num_splits > 1) {
         const long KN = (long)K * N;
         const int rgrid = (int)((KN + 255) / 256 < 4L * num_sms ? (KN + 255) / 256 : 4L * num_sms);
         gw_reduce_splits_kernel<<<rgrid, 256, 0, stream>>>(scratch, gw, KN, num_splits, kGradFactor);
-        if (cudaGetLastError() != cudaSuccess) return LUTGEMM_E_CUDA;
+        if (launch_status() != LUTGEMM_OK) return LUTGEMM_E_CUDA;
     }
     return LUTGEMM_OK;
 }
@@ -582,24 +582,25 @@ int transpose_codes(const uint8_t *a, uint8_t *at, int M, int K, int pitch, cons
         // every column m < M is written (M = B * Ho * Wo is a multiple of 16, so pitch == M)
         const int smem = (conv.H * conv.W + 15) & ~15;
         if (smem > 48 * 1024 &&
-            cudaFuncSetAttribute(transpose_codes_plane_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            !cuda_ok(cudaFuncSetAttribute(transpose_codes_plane_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
             return LUTGEMM_E_CUDA;
         transpose_codes_plane_kernel<<<conv.B * conv.C, 256, smem, stream>>>(a, at, pitch, conv);
-        return cudaGetLastError() == cudaSuccess ? LUTGEMM_OK : LUTGEMM_E_CUDA;
+        return launch_status();
     }
     const dim3 block(32, 32), grid((pitch / 16 + 31) / 32, (K + 31) / 32);
     if (grid.y > 65535u) return LUTGEMM_E_TOOLARGE;
     transpose_codes_kernel<<<grid, block, 0, stream>>>(a, at, M, K, pitch, conv);
-    return cudaGetLastError() == cudaSuccess ? LUTGEMM_OK : LUTGEMM_E_CUDA;
+    return launch_status();
 }
 
-int col2im_gather(const float *gcol, float *gx, const ConvGeom &g, cudaStream_t stream) {
+int col2im_gather(const float *gcol, float *gx, const ConvGeom &g, int num_sms, cudaStream_t stream) {
     const long total = (long)g.B * g.C * g.H * ((g.W + 3) / 4);
     const long blocks = (total + 255) / 256;
-    const int grid = (int)(blocks < 148L * 32 ? blocks : 148L * 32);
+    const long cap = (long)num_sms * 32;
+    const int grid = (int)(blocks < cap ? blocks : cap);
     if (g.stride == 1) col2im_gather_kernel<true><<<grid, 256, 0, stream>>>(gcol, gx, g);
     else col2im_gather_kernel<false><<<grid, 256, 0, stream>>>(gcol, gx, g);
-    return cudaGetLastError() == cudaSuccess ? LUTGEMM_OK : LUTGEMM_E_CUDA;
+    return launch_status();
 }
 
 }  // namespace lutgemm

@@ -189,8 +189,8 @@ static int launch_fwd(const uint8_t *a, const uint8_t *w, uint32_t *c, const uin
                       const ConvGeom &conv, int num_sms, cudaStream_t stream) {
     using Cfg = FwdCfg<BITS, R, C, WM, WN>;
     auto kern = fwd_rowbcast_kernel<BITS, R, C, WM, WN>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
-    if (e != cudaSuccess) return LUTGEMM_E_CUDA;
+    if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM)))
+        return LUTGEMM_E_CUDA;
     const int tiles_m = (M + Cfg::MT - 1) / Cfg::MT, tiles_n = (N + Cfg::NT - 1) / Cfg::NT;
     const long tiles = (long)tiles_m * tiles_n;
     const int ctas_per_sm = Cfg::SMEM <= 100 * 1024 ? 2 : 1;
@@ -199,7 +199,7 @@ static int launch_fwd(const uint8_t *a, const uint8_t *w, uint32_t *c, const uin
     const int vec_w = (N % 16 == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
     const int vec_c = (N % 4 == 0) && ((reinterpret_cast<uintptr_t>(c) & 15) == 0);
     kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(a, w, c, lut, M, K, N, tiles_m, tiles_n, vec_a, vec_w, vec_c, conv);
-    return cudaGetLastError() == cudaSuccess ? LUTGEMM_OK : LUTGEMM_E_CUDA;
+    return launch_status();
 }
 
 template <int BITS>

@@ -7,6 +7,17 @@
 
 namespace lutgemm {
 
+// Failure bookkeeping: the CUDA error behind a LUTGEMM_E_CUDA status is kept per host thread so that
+// lutgemm_status_string can name it (cudaGetLastError clears the runtime's own record).
+void record_cuda_error(cudaError_t e);
+inline bool cuda_ok(cudaError_t e) {
+    if (e == cudaSuccess) return true;
+    record_cuda_error(e);
+    return false;
+}
+// status of the launch just made on this thread
+int launch_status();
+
 struct ConvGeom;  // lutgemm_common.cuh; geometry.enabled == 0 means `a` is a plain [M,K] matrix
 
 int forward_rowbcast(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K,
@@ -36,17 +47,10 @@ int backward_gw_slab_tall(const float *gc, const uint8_t *a, const uint8_t *w, f
 int backward_ga_slab_tall(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, const int16_t *lut_ga,
                           int bits, int M, int K, int N, const ConvGeom &conv, float *scratch, int num_sms,
                           cudaStream_t stream);
-// warp-specialised variants of the three slab kernels (producer warps build slabs, consumer warps gather)
-int forward_slab_ws(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K,
-                    int N, int num_sms, cudaStream_t stream);
-int backward_gw_slab_ws(const float *gc, const uint8_t *a, const uint8_t *w, float *gw, const int16_t *lut_gw,
-                        int bits, int M, int K, int N, float *scratch, int num_sms, cudaStream_t stream);
-int backward_ga_slab_ws(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, const int16_t *lut_ga,
-                        int bits, int M, int K, int N, float *scratch, int num_sms, cudaStream_t stream);
-// reads (and clears) the device-side error word of the warp-specialised kernels; synchronises the device
-int slab_ws_read_and_clear_error(int *value);
+// reads (and clears) the device-side error word of the bounded barrier waits; synchronises the device
+int read_and_clear_device_error(int *value);
 // launches a one-warp kernel whose barrier wait can never be satisfied (it must time out with error id 99)
-int slab_ws_bounded_wait_selftest(cudaStream_t stream);
+int bounded_wait_selftest(cudaStream_t stream);
 // out[k][c] (or out[c][k] when transpose) = 1/16 * sum over row blocks of part[b][k][c], b ascending
 int slab_reduce_blocks(const float *part, float *out, int K, int C, int nblocks, bool transpose, int bkl_L,
                        int num_sms, cudaStream_t stream);
@@ -57,7 +61,7 @@ int slab_reduce_blocks(const float *part, float *out, int K, int C, int nblocks,
 int transpose_codes(const uint8_t *a, uint8_t *at, int M, int K, int pitch, const ConvGeom &conv, cudaStream_t stream);
 
 // gx[B,C,H,W] from the unfolded activation gradient gcol[B][C*kh*kw][Ho*Wo] (deterministic gather)
-int col2im_gather(const float *gcol, float *gx, const ConvGeom &g, cudaStream_t stream);
+int col2im_gather(const float *gcol, float *gx, const ConvGeom &g, int num_sms, cudaStream_t stream);
 
 // quantisation prologue / epilogue of an approximate convolution layer (lutgemm_quant.cu); strides in elements
 int quantize_codes(const float *x, long sb, long sc, long sh, long sw, int B, int C, int H, int W, const float *scale,

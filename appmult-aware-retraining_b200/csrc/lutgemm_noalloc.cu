@@ -11,6 +11,7 @@
 #include <mutex>
 
 #include "lutgemm.h"
+#include "lutgemm_kernels.h"
 
 namespace {
 
@@ -27,11 +28,11 @@ void *g_scratch_addr[kMaxDevices];  // per device, filled on the first call made
 // Address of the scratch array on the current device, or nullptr after recording the CUDA error.
 void *scratch_on_current_device() {
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    if (!lutgemm::cuda_ok(cudaGetDevice(&dev)) || dev < 0 || dev >= kMaxDevices) return nullptr;
     std::lock_guard<std::mutex> lock(g_setup_mutex);
     if (g_scratch_addr[dev]) return g_scratch_addr[dev];
     void *ptr = nullptr;
-    if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess || ptr == nullptr) return nullptr;
+    if (!lutgemm::cuda_ok(cudaGetSymbolAddress(&ptr, g_noalloc_scratch)) || ptr == nullptr) return nullptr;
     g_scratch_addr[dev] = ptr;
     return ptr;
 }

@@ -130,7 +130,7 @@ int quantize_codes(const float *x, long sb, long sc, long sh, long sw, int B, in
     const int grid = (int)(tiles < 16L * num_sms ? tiles : 16L * num_sms);
     quant_tile_kernel<false><<<grid, 256, 0, stream>>>(x, sb, sc, sh, sw, B, C, H, W, scale, zp_neg, qmax, codes, chansum,
                                                        nullptr, nullptr, nullptr, nullptr, nullptr);
-    return cudaGetLastError() == cudaSuccess ? LUTGEMM_OK : LUTGEMM_E_CUDA;
+    return launch_status();
 }
 
 int quantize_backward(const float *x, long sb, long sc, long sh, long sw, int B, int C, int H, int W, const float *scale,
@@ -140,7 +140,7 @@ int quantize_backward(const float *x, long sb, long sc, long sh, long sw, int B,
     const int grid = (int)(tiles < 16L * num_sms ? tiles : 16L * num_sms);
     quant_tile_kernel<true><<<grid, 256, 0, stream>>>(x, sb, sc, sh, sw, B, C, H, W, scale, zp_neg, qmax, nullptr, nullptr,
                                                       gcodes, boxT, s_w, z_w, gx);
-    return cudaGetLastError() == cudaSuccess ? LUTGEMM_OK : LUTGEMM_E_CUDA;
+    return launch_status();
 }
 
 int conv_epilogue(const uint32_t *y, const float *box, const float *sumw_t, const float *taps, const float *s_a,
@@ -149,7 +149,7 @@ int conv_epilogue(const uint32_t *y, const float *box, const float *sumw_t, cons
     const long blocks = (M * Cout + 255) / 256;
     const int grid = (int)(blocks < 32L * num_sms ? blocks : 32L * num_sms);
     conv_epilogue_kernel<<<grid, 256, 0, stream>>>(y, box, sumw_t, taps, s_a, s_w, z_a, z_w, bias, out, M, L, Cout);
-    return cudaGetLastError() == cudaSuccess ? LUTGEMM_OK : LUTGEMM_E_CUDA;
+    return launch_status();
 }
 
 }  // namespace lutgemm

@@ -223,7 +223,7 @@ static int launch_fwd_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, cons
                            const ConvGeom &conv, const uint8_t *at, int at_pitch, int num_sms, cudaStream_t stream) {
     using C = sf::Cfg<BITS>;
     auto kern = at ? sf::slab_fwd_kernel<BITS, true> : sf::slab_fwd_kernel<BITS, false>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
+    if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM)))
         return LUTGEMM_E_CUDA;
     sf::Args p{};
     p.a = a; p.w = w; p.lut = lut; p.c = c; p.M = M; p.K = K; p.N = N;
@@ -249,13 +249,13 @@ static int launch_fwd_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, cons
     p.k_per_split = ((kchunks + ksplits - 1) / ksplits) * C::KC;
     const long items = tiles * ksplits;
     const int grid = (int)(items < num_sms ? items : num_sms);
-    if (ksplits > 1 && cudaMemsetAsync(c, 0, (size_t)M * N * sizeof(uint32_t), stream) != cudaSuccess)
+    if (ksplits > 1 && !cuda_ok(cudaMemsetAsync(c, 0, (size_t)M * N * sizeof(uint32_t), stream)))
         return LUTGEMM_E_CUDA;
     p.vec_a = !conv.enabled && (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(a) & 15) == 0);
     p.vec_w = (N % 16 == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
     p.vec_c = (N % 2 == 0) && ((reinterpret_cast<uintptr_t>(c) & 7) == 0);
     kern<<<grid, C::THREADS, C::SMEM, stream>>>(p);
-    return cudaGetLastError() == cudaSuccess ? LUTGEMM_OK : LUTGEMM_E_CUDA;
+    return launch_status();
 }
 
 int forward_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K, int N,

@@ -395,7 +395,7 @@ int slab_reduce_blocks(const float *part, float *out, int K, int C, int nblocks,
         slab_reduce_blocks_kernel<true><<<rgrid, 256, 0, stream>>>(part, out, K, C, nblocks, kGradFactor, 0);
     else
         slab_reduce_blocks_kernel<false><<<rgrid, 256, 0, stream>>>(part, out, K, C, nblocks, kGradFactor, bkl_L);
-    return cudaGetLastError() == cudaSuccess ? LUTGEMM_OK : LUTGEMM_E_CUDA;
+    return launch_status();
 }
 
 template <int BITS, int MODE, int WARPS, int RW, int PF>
@@ -404,7 +404,7 @@ static int launch_slab_grad_w(const float *gc, const uint8_t *a, const uint8_t *
                             int at_pitch, int num_sms, cudaStream_t stream) {
     using C = sg::Cfg<BITS, WARPS, RW>;
     auto kern = sg::slab_grad_kernel<BITS, MODE, WARPS, RW, PF>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
+    if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM)))
         return LUTGEMM_E_CUDA;
     const int RDIM = MODE == sg::kGa ? N : M, CDIM = MODE == sg::kGa ? M : N;
     sg::Args p{};
@@ -438,7 +438,7 @@ static int launch_slab_grad_w(const float *gc, const uint8_t *a, const uint8_t *
     const long items = tiles * ksplits;
     const int grid = (int)(items < num_sms ? items : num_sms);
     kern<<<grid, C::THREADS, C::SMEM, stream>>>(p);
-    if (cudaGetLastError() != cudaSuccess) return LUTGEMM_E_CUDA;
+    if (launch_status() != LUTGEMM_OK) return LUTGEMM_E_CUDA;
     if (!p.direct)
         return slab_reduce_blocks(scratch, out, K, CDIM, p.tiles_r, MODE == sg::kGa, p.ga_bkl ? conv.Ho * conv.Wo : 0,
                                   num_sms, stream);

@@ -360,7 +360,7 @@ static int launch_slab_grad_tall(const float *gc, const uint8_t *a, const uint8_
     const bool use_at = MODE == sgt::kGw && at != nullptr;
     auto kern = use_at ? sgt::slab_grad_tall_kernel<BITS, MODE, 4, MODE == sgt::kGw>
                        : sgt::slab_grad_tall_kernel<BITS, MODE, 4, false>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
+    if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM)))
         return LUTGEMM_E_CUDA;
     const int RDIM = MODE == sgt::kGa ? N : M, CDIM = MODE == sgt::kGa ? M : N;
     sgt::Args p{};
@@ -394,7 +394,7 @@ static int launch_slab_grad_tall(const float *gc, const uint8_t *a, const uint8_
     const long items = tiles * ksplits;
     const int grid = (int)(items < num_sms ? items : num_sms);
     kern<<<grid, C::THREADS, C::SMEM, stream>>>(p);
-    if (cudaGetLastError() != cudaSuccess) return LUTGEMM_E_CUDA;
+    if (launch_status() != LUTGEMM_OK) return LUTGEMM_E_CUDA;
     if (!p.direct)
         return slab_reduce_blocks(scratch, out, K, CDIM, p.tiles_r, MODE == sgt::kGa, p.ga_bkl ? conv.Ho * conv.Wo : 0,
                                   num_sms, stream);

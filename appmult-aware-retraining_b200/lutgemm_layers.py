@@ -262,7 +262,7 @@ class _AppQuant(nn.Module):
 
 class AppConv2d(nn.Conv2d, _AppQuant):
     def __init__(self, in_channels, out_channels, kernel_size, stride=1, padding=0, dilation=1, groups=1, bias=True,
-                 a_bits=7, w_bits=7, use_ste_gradient=False, conv_impl="unfold"):
+                 a_bits=7, w_bits=7, use_ste_gradient=False, conv_impl="fused"):
         nn.Conv2d.__init__(self, in_channels, out_channels, kernel_size, stride, padding, dilation, groups, bias)
         assert groups == 1, "groups is not supported in approximate convolution"
         self._init_quant(a_bits, w_bits)
@@ -271,12 +271,11 @@ class AppConv2d(nn.Conv2d, _AppQuant):
 
     def _approx_conv(self, xq, wq):
         kw = dict(bias=None, stride=self.stride, padding=self.padding, dilation=self.dilation, groups=1)
+        if self.conv_impl == "unfold":  # the reference's F.unfold formulation, for comparisons
+            gemm = self_ops.approx_gemm_baseline_op if self.use_ste_gradient else self_ops.approx_gemm_op
+            return _ops_state.unfold_conv2d(gemm, xq, wq, **kw)
         if self.use_ste_gradient:
-            if self.conv_impl == "unfold":
-                return self_ops.approx_conv2d_baseline_op(xq, wq, **kw)
-            return self_ops.approx_conv2d_fused_baseline_op(xq, wq, **kw)
-        if self.conv_impl == "fused":
-            return self_ops.approx_conv2d_fused_op(xq, wq, **kw)
+            return self_ops.approx_conv2d_baseline_op(xq, wq, **kw)
         return self_ops.approx_conv2d_op(xq, wq, **kw)
 
     def forward(self, x):
@@ -332,7 +331,7 @@ class AppLinear(nn.Linear, _AppQuant):
 
 
 def prepare(model: nn.Module, a_bits: int = 7, w_bits: int = 7, use_ste_gradient: bool = False,
-            conv_impl: str = "unfold", linear: bool = True) -> nn.Module:
+            conv_impl: str = "fused", linear: bool = True) -> nn.Module:
     """Swaps every nn.Conv2d (and, with linear=True, nn.Linear) of `model` in place for its approximate
     counterpart; parameters are shared with the replaced module (cf. add_quant_op,
     micronet+/app_layers.py:270-339)."""

@@ -7,6 +7,7 @@ from .approx_ops import (
     approx_conv2d_baseline_op,
     approx_conv2d_fused_op,
     approx_conv2d_fused_baseline_op,
+    unfold_conv2d,
 )
 
 # the first five names are the reference's public API (self_ops/ops_py/__init__.py:1-12)
@@ -19,4 +20,5 @@ __all__ = [
     "set_lookup_tables",
     "approx_conv2d_fused_op",
     "approx_conv2d_fused_baseline_op",
+    "unfold_conv2d",
 ]

@@ -138,7 +138,10 @@ approx_gemm_op = ApproxGemm.apply
 approx_gemm_baseline_op = ApproxGemmBaseline.apply
 
 
-def _conv2d_via_gemm(gemm_op, input, weight, bias, stride, padding, dilation, groups):
+def unfold_conv2d(gemm_op, input, weight, bias, stride, padding, dilation, groups):
+    """The reference's formulation of the convolution (self_ops/ops_py/approx_ops.py:545-571): pad with code 0,
+    `F.unfold`, one LUT-GEMM on the materialised [B*Ho*Wo, Cin*kh*kw] matrix.  Kept as the comparison the
+    tests hold the fused kernels against; the public ops below do not use it."""
     assert bias is None, "bias is not supported in approximate convolution"
     assert groups == 1, "groups is not supported in approximate convolution"
     s, p, d = stride[0], padding[0], dilation[0]
@@ -153,21 +156,12 @@ def _conv2d_via_gemm(gemm_op, input, weight, bias, stride, padding, dilation, gr
     return out.view(B, Ho * Wo, Cout).transpose(1, 2).reshape(B, Cout, Ho, Wo)
 
 
-def approx_conv2d_op(input, weight, bias, stride, padding, dilation, groups):
-    """Approximate convolution of code tensors: input [B,Cin,H,W], weight [Cout,Cin,kh,kw] ->
-    [B,Cout,Ho,Wo]; bias must be None and groups 1 (reference approx_conv2d_op, :530-573)."""
-    return _conv2d_via_gemm(approx_gemm_op, input, weight, bias, stride, padding, dilation, groups)
-
-
-def approx_conv2d_baseline_op(input, weight, bias, stride, padding, dilation, groups):
-    """Same forward with the straight-through backward (reference approx_conv2d_baseline_op, :576-619)."""
-    return _conv2d_via_gemm(approx_gemm_baseline_op, input, weight, bias, stride, padding, dilation, groups)
-
-
 class ApproxConv2dFused(Function):
-    """Approximate convolution with the im2col fused into the kernels' operand loaders: neither the
-    unfolded activations nor their uint8 copy ever reach HBM in the forward pass (the reference
-    materialises both, :556-563).  Same values and gradients as `approx_conv2d_op`."""
+    """Approximate convolution on the convolution entry points of the library: the fp32 unfolded activations
+    the reference materialises twice (:556-563) never exist.  Large layers write ONE uint8 copy of the unfolded
+    codes, transposed ([K][M], a quarter of one fp32 unfold), which the forward and the weight-gradient kernels
+    both read; small layers gather the codes from the NCHW image inside the kernels' operand loaders.  Same
+    values and gradients as the reference's `approx_conv2d_op` (unfold + LUT-GEMM)."""
 
     @staticmethod
     def forward(ctx, input, weight, stride, padding, dilation):
@@ -202,17 +196,20 @@ class ApproxConv2dFused(Function):
         return gx, (gw.t().reshape(wshape) if gw is not None else None), None, None, None
 
 
-def approx_conv2d_fused_op(input, weight, bias, stride, padding, dilation, groups):
-    """Drop-in for `approx_conv2d_op` (same arguments and results) running on the fused kernels."""
+def approx_conv2d_op(input, weight, bias, stride, padding, dilation, groups):
+    """Approximate convolution of code tensors: input [B,Cin,H,W], weight [Cout,Cin,kh,kw] ->
+    [B,Cout,Ho,Wo]; bias must be None, groups 1, stride / padding / dilation square (their first entries are
+    used), as in the reference's approx_conv2d_op (:530-573), whose arguments, values and gradients this
+    reproduces without `F.unfold`."""
     assert bias is None, "bias is not supported in approximate convolution"
     assert groups == 1, "groups is not supported in approximate convolution"
     return ApproxConv2dFused.apply(input, weight, stride[0], padding[0], dilation[0])
 
 
 class ApproxConv2dFusedBaseline(Function):
-    """Straight-through variant of `ApproxConv2dFused`: the same fused LUT forward; the backward treats the
-    product as exact, i.e. the plain convolution gradients on the float codes (what `approx_conv2d_baseline_op`
-    computes through unfold + matmul, self_ops/ops_py/approx_ops.py:576-619 of the reference)."""
+    """Straight-through variant of `ApproxConv2dFused`: the same LUT forward; the backward treats the product
+    as exact, i.e. the plain convolution gradients on the float codes (what the reference computes through
+    unfold + matmul, self_ops/ops_py/approx_ops.py:576-619)."""
 
     @staticmethod
     def forward(ctx, input, weight, stride, padding, dilation):
@@ -235,16 +232,25 @@ class ApproxConv2dFusedBaseline(Function):
         input, weight = ctx.saved_tensors
         stride, padding, dilation = ctx.geom
         gx = gw = None
-        if ctx.needs_input_grad[0]:
-            gx = torch.nn.grad.conv2d_input(input.shape, weight, g_out, stride=stride, padding=padding, dilation=dilation)
-        if ctx.needs_input_grad[1]:
-            gw = torch.nn.grad.conv2d_weight(input, weight.shape, g_out, stride=stride, padding=padding, dilation=dilation)
+        # full fp32 like the reference's two matmuls (:259-260): no TF32 rounding of grad_out or of the codes
+        with torch.backends.cudnn.flags(enabled=True, allow_tf32=False):
+            if ctx.needs_input_grad[0]:
+                gx = torch.nn.grad.conv2d_input(input.shape, weight, g_out, stride=stride, padding=padding,
+                                                dilation=dilation)
+            if ctx.needs_input_grad[1]:
+                gw = torch.nn.grad.conv2d_weight(input, weight.shape, g_out, stride=stride, padding=padding,
+                                                 dilation=dilation)
         return gx, gw, None, None, None
 
 
-def approx_conv2d_fused_baseline_op(input, weight, bias, stride, padding, dilation, groups):
-    """Drop-in for `approx_conv2d_baseline_op` (same arguments and results up to fp32 summation order) with the
-    fused forward kernels."""
+def approx_conv2d_baseline_op(input, weight, bias, stride, padding, dilation, groups):
+    """Same forward with the straight-through backward (reference approx_conv2d_baseline_op, :576-619): the
+    gradients are those of an exact convolution of the float codes."""
     assert bias is None, "bias is not supported in approximate convolution"
     assert groups == 1, "groups is not supported in approximate convolution"
     return ApproxConv2dFusedBaseline.apply(input, weight, stride[0], padding[0], dilation[0])
+
+
+# earlier names of the two functions above
+approx_conv2d_fused_op = approx_conv2d_op
+approx_conv2d_fused_baseline_op = approx_conv2d_baseline_op

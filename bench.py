@@ -182,6 +182,103 @@ def run_reference_arm(args, rank, world):
 
 
 # ------------------------------------------------------------------------------------------------
+# checker legs of our arm: sampled parity gate against the C oracle, the reference's CUDA kernels beside ours
+# ------------------------------------------------------------------------------------------------
+def parity_gate(bits, s, lf, la, lw, nsample=16):
+    """Compares sampled rows and columns of one step's three results with the C oracle: forward bit-exact,
+    gradients within 1e-5 of the sum of the absolute terms of each element.  Returns a dict for the JSON line;
+    raises on a mismatch (nothing is timed on wrong results)."""
+    from oracle import OracleC
+    oc = OracleC()
+    try:
+        oc.set_num_threads(len(os.sched_getaffinity(0)))
+    except AttributeError:
+        oc.set_num_threads(os.cpu_count() or 1)
+    a, w, gc = s["a"].cpu().numpy(), s["w"].cpu().numpy(), s["gc"].cpu().numpy()
+    c, ga, gw = s["c"].cpu().numpy(), s["ga"].cpu().numpy(), s["gw"].cpu().numpy()
+    lf_n, la_n, lw_n = lf.cpu().numpy(), la.cpu().numpy(), lw.cpu().numpy()
+    M, K = a.shape
+    N = w.shape[1]
+    pick = lambda n: np.unique(np.linspace(0, n - 1, min(nsample, n)).astype(np.int64))
+    ms, ks, ns = pick(M), pick(K), pick(N)
+    checked = 0
+
+    def close(got, ref, refabs, what):
+        nonlocal checked
+        bad = np.abs(got - ref) > 1e-5 * refabs + 1e-30
+        if bad.any() or not np.isfinite(got).all():
+            raise SystemExit(f"parity gate failed: {what}: {int(bad.sum())} of {bad.size} sampled entries off")
+        checked += got.size
+
+    # forward: sampled rows and sampled columns, bit-exact
+    for got, ref, what in ((c[ms], oc.forward(a[ms], w, lf_n, bits), "forward rows"),
+                           (c[:, ns], oc.forward(a, w[:, ns], lf_n, bits), "forward columns")):
+        if not np.array_equal(got, ref):
+            raise SystemExit(f"parity gate failed: {what} differ from the oracle")
+        checked += got.size
+    # grad_a rows (their sum over n is complete for a row subset)
+    r_ga, _, r_gaa, _ = oc.backward_f64(gc[ms], a[ms], w, la_n, lw_n, bits)
+    close(ga[ms], r_ga, r_gaa, "grad_a rows")
+    # a k subset gives grad_a columns and grad_w rows, both complete sums
+    r_ga, r_gw, r_gaa, r_gwa = oc.backward_f64(gc, a[:, ks], w[ks], la_n, lw_n, bits)
+    close(ga[:, ks], r_ga, r_gaa, "grad_a columns")
+    close(gw[ks], r_gw, r_gwa, "grad_w rows")
+    # an n subset gives grad_w columns
+    _, r_gw, _, r_gwa = oc.backward_f64(gc[:, ns], a, w[:, ns], la_n, lw_n, bits)
+    close(gw[:, ns], r_gw, r_gwa, "grad_w columns")
+    return {"status": "ok", "entries_checked": int(checked),
+            "what": f"{len(ms)} rows and {len(ns)} columns of c (bit-exact), {len(ms)} rows / {len(ks)} columns of grad_a, "
+                    f"{len(ks)} rows / {len(ns)} columns of grad_w (1e-5 of the sum of absolute terms) against the C oracle"}
+
+
+def reference_cuda_leg(bits, s, lf, la, lw, reps=2):
+    """The reference's own CUDA kernels (built unmodified for sm_100a into oracle/_ref by
+    oracle/build_reference_ext.py) timed on the same inputs in this process, and their results compared with
+    ours.  Checker leg: returns a dict for the JSON line, or why it is unavailable."""
+    import glob
+    import importlib.util
+    import torch
+    hits = glob.glob(os.path.join(ROOT, "oracle", "_ref", f"approx_ops_ref{bits}*.so"))
+    if not hits:
+        return {"unavailable": f"oracle/_ref/approx_ops_ref{bits} is not built (the reference fixes the bit-width at "
+                               "compile time; modules exist for 7 and 8 bits where a reference checkout was at hand)"}
+    try:
+        spec = importlib.util.spec_from_file_location(f"approx_ops_ref{bits}", hits[0])
+        ref = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(ref)
+    except Exception as e:  # e.g. built against another PyTorch
+        return {"unavailable": f"could not load {os.path.basename(hits[0])}: {e}"}
+    a, w, gc = s["a"], s["w"], s["gc"]
+    c = torch.zeros_like(s["c"])
+    ga, gw = torch.zeros_like(s["ga"]), torch.zeros_like(s["gw"])
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    ref.approx_gemm_forward(a, w, c, lf)  # warm-up
+    ref.approx_gemm_backward(gc, a, w, ga, gw, la, lw)
+    torch.cuda.synchronize()
+    fwd_ms = bwd_ms = 0.0
+    for _ in range(reps):
+        ev[0].record()
+        ref.approx_gemm_forward(a, w, c, lf)
+        ev[1].record()
+        ref.approx_gemm_backward(gc, a, w, ga, gw, la, lw)
+        ev[2].record()
+        torch.cuda.synchronize()
+        fwd_ms += ev[0].elapsed_time(ev[1]) / reps
+        bwd_ms += ev[1].elapsed_time(ev[2]) / reps
+    M, K = a.shape
+    N = w.shape[1]
+    out = {"kind": "the reference's unmodified kernels compiled for sm_100a (legacy default stream, texture gathers at 8 bits)",
+           "forward_ms": fwd_ms, "backward_ms": bwd_ms, "ms_per_step": fwd_ms + bwd_ms,
+           "value": 3.0 * M * K * N / ((fwd_ms + bwd_ms) * 1e-3) / 1e9, "unit": "G LUT-MAC/s", "reps": reps}
+    # at 8 bits the reference adds LUT[0][0] per padded k when K is not a multiple of 8; otherwise results agree
+    if bits < 8 or K % 8 == 0:
+        out["forward_equal_to_ours"] = bool(torch.equal(c.view(torch.int32), s["c"].view(torch.int32)))
+        for name, r, o in (("grad_a", ga, s["ga"]), ("grad_w", gw, s["gw"])):
+            out[f"{name}_max_rel_diff_to_ours"] = float((r - o).abs().max() / r.abs().max().clamp_min(1e-30))
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------
 def run_ours(args, rank, world, local_rank):
@@ -195,8 +292,6 @@ def run_ours(args, rank, world, local_rank):
     lib = approx_ops.library()
     dev = torch.device(f"cuda:{local_rank}")
     torch.cuda.set_device(dev)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
 
     bits, S = args.bits, args.size
     K = N = S
@@ -227,9 +322,6 @@ def run_ours(args, rank, world, local_rank):
     scratch = torch.empty(max(1, scratch_bytes), dtype=torch.uint8, device=dev)
     fwd_ws_bytes = lib.lutgemm_forward_scratch_bytes(bits, M, K, N)  # transposed activation codes
     fwd_ws = torch.empty(max(1, fwd_ws_bytes), dtype=torch.uint8, device=dev)
-    # + the code transposition and the two block-reduce kernels of the slab path, or the split-M reduce kernel
-    # (the transposition runs once per step: the grad_w kernel reuses the forward pass's copy)
-    launches_per_step = 3 + ((2 if bits >= 7 else 1) if scratch_bytes else 0) + (1 if fwd_ws_bytes else 0)
     stream = torch.cuda.current_stream(dev)
 
     def fwd(s):
@@ -267,6 +359,12 @@ def run_ours(args, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # parity gate before anything is timed: one step's results, sampled, against the C oracle (rank 0)
+    gate = None
+    step(0)
+    torch.cuda.synchronize()
+    if rank == 0 and not args.no_parity_gate:
+        gate = parity_gate(bits, sets[0], lf, la, lw)
     for i in range(args.warmup):
         step(i)
     barrier()
@@ -277,10 +375,12 @@ def run_ours(args, rank, world, local_rank):
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    launches_before = lib.lutgemm_kernel_launches()
     t_begin.record()
     for i in range(args.steps):
         step(i, evs[i])
     t_end.record()
+    launches = lib.lutgemm_kernel_launches() - launches_before  # counted by the library, not estimated
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     total_ms = t_begin.elapsed_time(t_end)
@@ -352,9 +452,7 @@ def run_ours(args, rank, world, local_rank):
     d2h = 4 * M * N + 4 * M * K + 4 * K * N
 
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
+        return None
 
     macs_step = 3.0 * M * K * N
     value = world * macs_step * args.steps / (total_ms * 1e-3) / 1e9
@@ -379,12 +477,16 @@ def run_ours(args, rank, world, local_rank):
         "per_kernel_ms": {n: float(t) for n, t in zip(names, kern_ms)},
         "hbm": {"achieved_gbs": alg_bytes[dom] / (kern_ms[dom] * 1e-3) / 1e9, "peak_gbs": peaks["hbm_gbs"],
                 "frac": alg_bytes[dom] / (kern_ms[dom] * 1e-3) / 1e9 / peaks["hbm_gbs"], "of": peaks_kind},
-        # dram__bytes_read.sum + dram__bytes_write.sum per launch of that kernel from the ncu capture
-        # summarised in profiles/slab_kernels_b8_4096.md (only that configuration was captured)
-        "traffic": ({"forward": 118.0e6, "grad_w": 360.8e6, "grad_a": 358.3e6}[names[dom]]
-                    if (bits, S, M) == (8, 4096, 4096) else None),
-        "traffic_unit": "bytes per launch (ncu, 8-bit 4096^3)",
+        # dram__bytes_read.sum + dram__bytes_write.sum per launch of that kernel: a property of the kernel and the
+        # problem size taken from a separate ncu capture (a profiler cannot run inside a timed run), so it is given
+        # only for the one configuration that was captured, with the capture named
+        "traffic": NCU_DRAM_TRAFFIC["bytes_per_launch"].get(names[dom]) if (bits, S, M) == NCU_DRAM_TRAFFIC["config"] else None,
+        "traffic_source": NCU_DRAM_TRAFFIC["source"] if (bits, S, M) == NCU_DRAM_TRAFFIC["config"] else None,
+        "algorithmic_bytes": alg_bytes[dom],
     }
+    ref_cuda = None
+    if world == 1 and not args.no_reference_cuda:
+        ref_cuda = reference_cuda_leg(bits, sets[0], lf, la, lw)
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
@@ -404,15 +506,13 @@ def run_ours(args, rank, world, local_rank):
                                 else f"lutgemm fwd+bwd {bits}-bit M=K=N={S} per GPU"), "bits": bits, "M_per_gpu": M, "K": K,
                    "N": N, "parallelism": f"dp{world} (M sharded, NCCL all-reduce of grad_w)" if world > 1 else "single GPU",
                    "l2": f"{nsets} rotating input/output sets; a step touches {(h2d + d2h) / 2**20:.0f} MiB > L2"},
-        "roofline": roofline, "cpu_baseline": cpu,
+        "roofline": roofline, "cpu_baseline": cpu, "parity_gate": gate, "reference_cuda": ref_cuda,
         "e2e": {"value": e2e_value, "unit": "G LUT-MAC/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
                 "copies": "inside the timed region, double-buffered on two side streams against the kernels"},
-        "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+        "gpu_launches": int(launches), "clocks": clocks,
     }
-    print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    return line
 
 
 # ------------------------------------------------------------------------------------------------
@@ -430,11 +530,9 @@ def run_model(args, rank, world, local_rank):
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device for --impl ours (there is no CPU fallback)")
-    approx_ops.library()
+    lib = approx_ops.library()
     dev = torch.device(f"cuda:{local_rank}")
     torch.cuda.set_device(dev)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
     bits, batch = args.bits, args.batch
     L, qa, qb = synthetic_wire_tables(bits, 0)
     self_ops.set_lookup_tables(dev, L, qa, qb, bits)
@@ -465,10 +563,12 @@ def run_model(args, rank, world, local_rank):
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    launches_before = lib.lutgemm_kernel_launches()
     e0.record()
     for i in range(args.steps):
         step(imgs_d[i % nsets], lbls_d[i % nsets])
     e1.record()
+    launches = lib.lutgemm_kernel_launches() - launches_before
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     total_ms = e0.elapsed_time(e1)
@@ -489,9 +589,7 @@ def run_model(args, rank, world, local_rank):
         total_ms, e2e_ms = float(t[0]), float(t[1])
     err = approx_ops.device_error()
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
+        return None
     peaks, peaks_kind = measured_peaks()
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
     clk_max = float(peaks.get("sm_max_mhz") or 1965.0)
@@ -516,16 +614,84 @@ def run_model(args, rank, world, local_rank):
         "e2e": {"value": world * batch * e2e_steps / (e2e_ms * 1e-3), "unit": "img/s",
                 "h2d_bytes_per_step": batch * (int(np.prod(image_shape)) * 4 + 8), "d2h_bytes_per_step": 4, "steps": e2e_steps,
                 "ms_per_step": e2e_ms / e2e_steps, "last_loss": loss_value},
-        "gpu_launches": None, "clocks": clocks, "device_error": err,
+        "gpu_launches": int(launches), "clocks": clocks, "device_error": err,
     }
-    print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    return line
 
+
+# ------------------------------------------------------------------------------------------------
+# per-layer timing of the ResNet-18 (CIFAR shape) convolutions through the convolution entry points
+# ------------------------------------------------------------------------------------------------
+# name, Cin, H = W, Cout, kernel, stride, pad, occurrences in the network
+RESNET18_LAYERS = [("stem", 3, 32, 64, 3, 1, 1, 1), ("s1", 64, 32, 64, 3, 1, 1, 4), ("s2a", 64, 32, 128, 3, 2, 1, 1),
+                   ("s2", 128, 16, 128, 3, 1, 1, 3), ("s2sc", 64, 32, 128, 1, 2, 0, 1), ("s3a", 128, 16, 256, 3, 2, 1, 1),
+                   ("s3", 256, 8, 256, 3, 1, 1, 3), ("s3sc", 128, 16, 256, 1, 2, 0, 1), ("s4a", 256, 8, 512, 3, 2, 1, 1),
+                   ("s4", 512, 4, 512, 3, 1, 1, 3), ("s4sc", 256, 8, 512, 1, 2, 0, 1)]
+
+
+def run_layers(args, local_rank):
+    """--workload resnet18_layers: every distinct convolution of the network on its own - forward, grad_w and
+    grad_x in ms (CUDA events) and as a fraction of the look-up roofline, plus per-step totals weighted by how
+    often the layer occurs.  Each call is timed alone, so grad_w includes the code transposition that a
+    training step shares with the forward pass."""
+    import torch
+
+    import approx_ops
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+    bits, B = args.bits, args.batch
+    L, qa, qb = synthetic_wire_tables(bits, 0)
+    lf = torch.from_numpy(pack_wire(L, bits, np.uint16)).to(dev)
+    la = torch.from_numpy(pack_wire(qa, bits, np.int16)).to(dev)
+    lw = torch.from_numpy(pack_wire(qb, bits, np.int16)).to(dev)
+    peaks, peaks_kind = measured_peaks()
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    roof = sms * float(peaks.get("sm_max_mhz") or 1965.0) * 1e6 * LSU_LOOKUPS_PER_CLK_PER_SM
+
+    def timeit(fn, reps=3):
+        fn(); fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    rows, tot = [], [0.0, 0.0, 0.0]
+    for name, cin, hw, cout, k, st, p, cnt in RESNET18_LAYERS:
+        x = torch.randint(0, 1 << bits, (B, cin, hw, hw), dtype=torch.uint8, device=dev)
+        wm = torch.randint(0, 1 << bits, (cin * k * k, cout), dtype=torch.uint8, device=dev)
+        ho = (hw + 2 * p - k) // st + 1
+        M, K = B * ho * ho, cin * k * k
+        y = torch.empty(M, cout, dtype=torch.uint32, device=dev)
+        gy = torch.randn(M, cout, device=dev)
+        gx, gw = torch.empty(B, cin, hw, hw, device=dev), torch.empty(K, cout, device=dev)
+        tf = timeit(lambda: approx_ops.approx_conv2d_forward(x, wm, y, lf, k, k, st, p, 1))
+        tw = timeit(lambda: approx_ops.approx_conv2d_backward(gy, x, wm, None, gw, la, lw, k, k, st, p, 1))
+        tx = timeit(lambda: approx_ops.approx_conv2d_backward(gy, x, wm, gx, None, la, lw, k, k, st, p, 1)) if name != "stem" else 0.0
+        look = float(M) * K * cout
+        frac = lambda t: look / (t * 1e-3) / roof if t > 0 else None
+        rows.append({"layer": name, "M": M, "K": K, "N": cout, "count": cnt, "forward_ms": tf, "forward_frac": frac(tf),
+                     "grad_w_ms": tw, "grad_w_frac": frac(tw), "grad_x_ms": tx, "grad_x_frac": frac(tx)})
+        for i, t in enumerate((tf, tw, tx)):
+            tot[i] += t * cnt
+    return {"metric": "appmult_resnet18_layer_times", "unit": "ms", "bits": bits, "batch": B, "layers": rows,
+            "per_step_ms": {"forward": tot[0], "grad_w": tot[1], "grad_x": tot[2], "sum": sum(tot)},
+            "roofline_peak": roof / 1e9, "roofline_unit": "G lookups/s", "peak_of": peaks_kind}
+
+
+# DRAM traffic of the three main kernels from the ncu capture summarised under profiles/ (bytes per launch)
+NCU_DRAM_TRAFFIC = {
+    "config": (8, 4096, 4096),
+    "bytes_per_launch": {"forward": 118.0e6, "grad_w": 360.8e6, "grad_a": 358.3e6},
+    "source": "ncu --set full capture of one launch per kernel, 8-bit 4096^3 (profiles/slab_kernels_b8_4096.md)",
+}
 
 WORKLOAD_NAMES = {"resnet18": "ResNet-18 CIFAR-shape", "resnet50": "ResNet-50 ImageNet-shape", "vit_s": "ViT-S/16"}
 # per-workload defaults of the benchmark configurations: (bits, per-GPU batch)
-WORKLOAD_DEFAULTS = {"resnet18": (7, 256), "resnet50": (8, 128), "vit_s": (7, 64)}
+WORKLOAD_DEFAULTS = {"resnet18": (7, 256), "resnet50": (8, 128), "vit_s": (7, 64), "resnet18_layers": (7, 256)}
 
 
 def main():
@@ -537,12 +703,17 @@ def main():
     ap.add_argument("--bits", type=int, default=8, choices=[4, 6, 7, 8])
     ap.add_argument("--size", type=int, default=4096)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", choices=["lutgemm", "resnet18", "resnet50", "vit_s"], default="lutgemm")
+    ap.add_argument("--workload", choices=["lutgemm", "resnet18", "resnet50", "vit_s", "resnet18_layers"], default="lutgemm")
     ap.add_argument("--batch", type=int, default=None, help="per-GPU batch of the model workloads")
     ap.add_argument("--conv-impl", choices=["layer", "fused", "unfold"], default="layer")
     ap.add_argument("--shard-m", action="store_true",
                     help="lutgemm workload: cut the M rows of ONE size^3 problem across the ranks (strong scaling)")
     ap.add_argument("--ste", action="store_true", help="model workloads: straight-through backward instead of the gradient tables")
+    ap.add_argument("--no-parity-gate", action="store_true", help="lutgemm workload: skip the sampled oracle comparison")
+    ap.add_argument("--no-reference-cuda", action="store_true",
+                    help="lutgemm workload: do not time the reference's own CUDA kernels beside ours")
+    ap.add_argument("--no-model", action="store_true",
+                    help="lutgemm workload: do not append the ResNet-18 training-step measurement")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -550,14 +721,40 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference_arm(args, rank, world)
-    elif args.workload != "lutgemm":
+        return
+    import torch
+    import torch.distributed as dist
+    if world > 1:
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    if args.workload != "lutgemm":
         if "--bits" not in sys.argv:
             args.bits = WORKLOAD_DEFAULTS[args.workload][0]
         if args.batch is None:
             args.batch = WORKLOAD_DEFAULTS[args.workload][1]
-        run_model(args, rank, world, local_rank)
+        if args.workload == "resnet18_layers":
+            line = run_layers(args, local_rank) if rank == 0 else None
+        else:
+            line = run_model(args, rank, world, local_rank)
     else:
-        run_ours(args, rank, world, local_rank)
+        line = run_ours(args, rank, world, local_rank)
+        if not args.no_model and not args.shard_m:
+            # the second half of the metric on the same GPUs in the same run: the ResNet-18 (CIFAR shape) AppMult
+            # training step of benchmark configuration 1 - 7-bit, batch 256 per GPU, SGD
+            import gc
+            gc.collect()
+            torch.cuda.empty_cache()
+            margs = argparse.Namespace(**vars(args))
+            margs.workload, margs.bits, margs.batch = "resnet18", WORKLOAD_DEFAULTS["resnet18"][0], WORKLOAD_DEFAULTS["resnet18"][1]
+            margs.steps, margs.warmup = max(5, min(args.steps, 20)), 3
+            mline = run_model(margs, rank, world, local_rank)
+            if line is not None:
+                line["resnet18"] = {k: mline[k] for k in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step",
+                                                          "scaling", "config", "roofline", "e2e", "gpu_launches", "clocks")}
+    if line is not None:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

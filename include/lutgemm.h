@@ -34,8 +34,29 @@ extern "C" {
 /* Library version (major*10000 + minor*100 + patch). */
 int lutgemm_version(void);
 
-/* Human-readable text for a status code; for LUTGEMM_E_CUDA the last CUDA error string of the
- * calling thread is appended.  The returned pointer is valid until the thread's next call. */
+/* Number of kernels this library has launched in this process so far (all entry points, all threads):
+ * the difference of two readings counts the launches in between.  No counterpart in the reference. */
+unsigned long long lutgemm_kernel_launches(void);
+
+/*
+ * Kernel-family override, process-wide; 0 (LUTGEMM_KERNEL_AUTO) in every position restores the automatic
+ * choice by problem shape, which is the default.  Meant for tests that must reach every kernel family on one
+ * shape and for A/B timing; results do not depend on it (forward bit-identical, gradients within fp32
+ * summation order).  forward: row-broadcast or slab kernel; backward: broadcast or slab gradient kernels;
+ * grad_tile: 512 x 64 or 1024 x 32 slab tile.  Call the *_scratch_bytes functions after changing it.
+ * No counterpart in the reference (one kernel per operator there).
+ */
+#define LUTGEMM_KERNEL_AUTO 0
+#define LUTGEMM_FORWARD_ROWBCAST 1
+#define LUTGEMM_FORWARD_SLAB 2
+#define LUTGEMM_BACKWARD_BCAST 1
+#define LUTGEMM_BACKWARD_SLAB 2
+#define LUTGEMM_TILE_WIDE 1
+#define LUTGEMM_TILE_TALL 2
+int lutgemm_set_kernel_choice(int forward, int backward, int grad_tile);
+
+/* Human-readable text for a status code; for LUTGEMM_E_CUDA the CUDA error behind the calling thread's
+ * last such status is appended.  The returned pointer is valid until the thread's next call. */
 const char *lutgemm_status_string(int status);
 
 /* Padded flat table length for a bit-width, or LUTGEMM_E_BITS.

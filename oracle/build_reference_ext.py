@@ -7,8 +7,8 @@ The reference fixes the bit-width with an unconditional `#define QUANTIZATION_BI
 (self_ops/src/approx_mult.h:12), so for every width the five source files are copied to a temporary
 directory, that one line is rewritten there, and the copy is compiled under a distinct module name
 (approx_ops_ref7, approx_ops_ref8).  Nothing of the reference is copied into this repository: only the
-built shared objects land in oracle/_ref/ (git-ignored).  Needs the development container (reference
-checkout + nvcc + the PyTorch headers); the GPU box only loads the prebuilt files.
+built shared objects land in oracle/_ref/ (git-ignored).  Building needs a reference checkout, nvcc and the
+PyTorch headers; running needs only the built modules and a GPU.
 TEST INFRASTRUCTURE: nothing in the product path imports these modules."""
 import os
 import re

@@ -1,6 +1,6 @@
 """Generates the golden fixtures under tests/golden/ from the reference's own Python layer.
 
-Run in the development container only (it reads the reference checkout, which does not travel):
+Needs a checkout of the reference project (the fixtures it writes are what the tests read):
 
     python tests/golden/make_golden.py [/path/to/reference]
 

@@ -167,20 +167,26 @@ def test_reduced_models_take_a_training_step(dev, name, kw, shape, bits):
 
 
 @pytest.mark.parametrize("bits", [7, 8])
-def test_whole_layer_linear_matches_the_autograd_expression(dev, bits):
-    """AppLinear with impl="layer" against the op-by-op expression (impl="ops"), 3-D token input, with bias."""
+def test_whole_layer_linear_matches_the_reference_expression(dev, bits):
+    """AppLinear with impl="layer" against the reference's layer expression carried over to a linear layer
+    (tests/reference_expression.py: LUT-GEMM product term plus three exact cross-term products, evaluated by
+    autograd), 3-D token input, with bias."""
     import self_ops
     from lutgemm_layers import AppLinear
+    from reference_expression import approx_linear_layer
     fp, ga, gb = O.synthetic_tables(bits, seed=70 + bits)
     self_ops.set_lookup_tables(dev, fp, ga, gb, bits)
     for s_, (B, T, K, N, bias) in enumerate([(2, 197, 384, 96, True), (3, 5, 33, 17, False), (1, 600, 64, 64, True)]):
         torch.manual_seed(10 * bits + s_)
-        ref = AppLinear(K, N, bias, bits, bits, False, "ops").to(dev).train()
         new = AppLinear(K, N, bias, bits, bits, False, "layer").to(dev).train()
-        new.load_state_dict(ref.state_dict())
         x = torch.randn(B, T, K, device=dev) * 1.3 - 0.2
         xr, xn = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
-        yr, yn = ref(xr), new(xn)
+        yn = new(xn)  # refreshes the layer's scales and zero points from this input
+        w_ref = new.weight.detach().clone().requires_grad_(True)
+        b_ref = new.bias.detach().clone().requires_grad_(True) if bias else None
+        yr = approx_linear_layer(self_ops.approx_gemm_op, xr.reshape(-1, K), w_ref, b_ref, new.activation_scale,
+                                 new.activation_zp_neg, new.weight_scale, new.weight_zp_neg, new.a_qmax,
+                                 new.w_qmax).reshape(B, T, N)
         qmax = float((1 << bits) - 1)
         s_a, z_a, s_w, z_w = (float(t) for t in (new.activation_scale, new.activation_zp_neg, new.weight_scale,
                                                   new.weight_zp_neg))
@@ -191,8 +197,8 @@ def test_whole_layer_linear_matches_the_autograd_expression(dev, bits):
         yn.backward(g)
         g2 = g.reshape(-1, N)
         cross = {"x": abs(s_w * z_w) * float(g2.sum(dim=1).abs().max()), "w": abs(s_a * z_a) * float(g2.sum(dim=0).abs().max())}
-        for a_, b_, name in ((xr.grad, xn.grad, "x"), (ref.weight.grad, new.weight.grad, "w")):
+        for a_, b_, name in ((xr.grad, xn.grad, "x"), (w_ref.grad, new.weight.grad, "w")):
             scale_ = float(a_.abs().max()) + 2.0 * cross[name]
             assert float((a_ - b_).abs().max()) <= 1e-5 * scale_ + 1e-30, (bits, s_, name)
         if bias:
-            assert torch.allclose(ref.bias.grad, new.bias.grad, rtol=1e-5, atol=1e-6)
+            assert torch.allclose(b_ref.grad, new.bias.grad, rtol=1e-5, atol=1e-6)

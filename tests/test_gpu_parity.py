@@ -97,28 +97,32 @@ def test_ragged_shapes_all_bit_widths(dev, oracle_c, bits):
         check_backward(oracle_c, gc, a, w, la, lw, bits, ga, gw)
 
 
-@pytest.mark.parametrize("kernel", ["rowbcast", "slab", "slab-ws"])
+@pytest.fixture
+def kernel_choice():
+    """approx_ops.set_kernel_choice for the duration of one test; the automatic choice is restored afterwards."""
+    import approx_ops
+    yield approx_ops.set_kernel_choice
+    approx_ops.set_kernel_choice()
+
+
+@pytest.mark.parametrize("kernel", ["rowbcast", "slab"])
 @pytest.mark.parametrize("bits", [4, 6, 7, 8])
-def test_each_forward_kernel_on_every_shape_class(dev, oracle_c, bits, kernel, monkeypatch):
-    """Every forward kernel (selected through LUTGEMM_FORWARD_KERNEL / LUTGEMM_SLAB_IMPL) must be bit-exact
-    on shapes the dispatcher would normally send to another one, including tiles that are almost empty."""
-    monkeypatch.setenv("LUTGEMM_FORWARD_KERNEL", kernel.split("-")[0])
-    monkeypatch.setenv("LUTGEMM_SLAB_IMPL", "ws" if kernel.endswith("-ws") else "sync")
+def test_each_forward_kernel_on_every_shape_class(dev, oracle_c, bits, kernel, kernel_choice):
+    """Every forward kernel (selected through lutgemm_set_kernel_choice) must be bit-exact on shapes the
+    dispatcher would normally send to another one, including tiles that are almost empty."""
+    kernel_choice(forward=kernel)
     lf, _, _ = synth_wire(bits, seed=10 + bits)
     for s, (M, K, N) in enumerate([(1, 1, 1), (5, 33, 3), (130, 16, 64), (515, 31, 67), (1024, 48, 128), (600, 257, 65)]):
         a, w, _ = rand_problem(bits, M, K, N, seed=7 * bits + s)
         assert np.array_equal(run_forward(dev, a, w, lf), oracle_c.forward(a, w, lf, bits)), (kernel, bits, M, K, N)
 
 
-@pytest.mark.parametrize("kernel", ["bcast", "slab-f32", "slab-tall", "slab-ws"])
+@pytest.mark.parametrize("kernel", ["bcast", "slab-wide", "slab-tall"])
 @pytest.mark.parametrize("bits", [4, 6, 7, 8])
-def test_each_backward_kernel_on_every_shape_class(dev, oracle_c, bits, kernel, monkeypatch):
-    """Every family of gradient kernels (LUTGEMM_BACKWARD_KERNEL / LUTGEMM_SLAB_IMPL / LUTGEMM_GRAD_TILE:
-    fp32 slab with the 512 x 64 and the 1024 x 32 tile, warp-specialised int16 slab, broadcast) on shapes
-    of either class."""
-    monkeypatch.setenv("LUTGEMM_BACKWARD_KERNEL", kernel.split("-")[0])
-    monkeypatch.setenv("LUTGEMM_SLAB_IMPL", "ws" if kernel.endswith("-ws") else "f32")
-    monkeypatch.setenv("LUTGEMM_GRAD_TILE", "tall" if kernel.endswith("-tall") else "wide")
+def test_each_backward_kernel_on_every_shape_class(dev, oracle_c, bits, kernel, kernel_choice):
+    """Every family of gradient kernels (selected through lutgemm_set_kernel_choice: fp32 slab with the
+    512 x 64 and the 1024 x 32 tile, broadcast) on shapes of either class."""
+    kernel_choice(backward=kernel.split("-")[0], grad_tile="tall" if kernel.endswith("-tall") else "wide")
     _, la, lw = synth_wire(bits, seed=20 + bits)
     shapes = [(1, 1, 1), (5, 33, 3), (130, 16, 64), (515, 31, 67), (1024, 48, 128), (66, 35, 520)]
     if kernel.endswith("-tall"):
@@ -225,13 +229,12 @@ CONV_CASES = [  # B, Cin, H, W, Cout, k, stride, pad, dil
 
 @pytest.mark.parametrize("bits", [4, 6, 7, 8])
 @pytest.mark.parametrize("tile", ["auto", "tall"])
-def test_fused_conv_kernels_against_oracle(dev, oracle_c, bits, tile, monkeypatch):
+def test_fused_conv_kernels_against_oracle(dev, oracle_c, bits, tile, kernel_choice):
     """lutgemm_conv2d_forward / _backward (implicit im2col) against im2col + GEMM + col2im on the oracle;
     once with the dispatcher's own choice and once with the tall-tile slab gradient kernels forced."""
     import approx_ops
     if tile == "tall":
-        monkeypatch.setenv("LUTGEMM_BACKWARD_KERNEL", "slab")
-        monkeypatch.setenv("LUTGEMM_GRAD_TILE", "tall")
+        kernel_choice(backward="slab", grad_tile="tall")
     lf, la, lw = synth_wire(bits, seed=30 + bits)
     lft, lat, lwt = (torch.from_numpy(t).to(dev) for t in (lf, la, lw))
     for s_, (B, Cin, H, W, Cout, k, st, p, d) in enumerate(CONV_CASES):
@@ -261,7 +264,8 @@ def test_fused_conv_kernels_against_oracle(dev, oracle_c, bits, tile, monkeypatc
 
 
 def test_fused_conv_op_against_golden(dev, golden):
-    """self_ops.approx_conv2d_fused_op must reproduce the golden conv fixtures like approx_conv2d_op does."""
+    """self_ops.approx_conv2d_op (convolution entry points of the library, no F.unfold) must reproduce the golden
+    conv fixtures, which the reference's own unfold-based Python layer produced."""
     import self_ops
     bits = int(golden["bits"])
     fp, ga_t, gb_t = (O.unpack_padded(golden[k], bits) for k in ("lut_fp", "lut_ga", "lut_gb"))
@@ -270,7 +274,7 @@ def test_fused_conv_op_against_golden(dev, golden):
         B, Cin, H, W, Cout, k, s, p, d = [int(v) for v in golden[f"conv{i}_cfg"]]
         x = torch.from_numpy(golden[f"conv{i}_x"]).to(dev).float().requires_grad_(True)
         wt = torch.from_numpy(golden[f"conv{i}_w"]).to(dev).float().requires_grad_(True)
-        y = self_ops.approx_conv2d_fused_op(x, wt, bias=None, stride=(s, s), padding=(p, p), dilation=(d, d), groups=1)
+        y = self_ops.approx_conv2d_op(x, wt, bias=None, stride=(s, s), padding=(p, p), dilation=(d, d), groups=1)
         assert np.array_equal(y.detach().cpu().numpy(), golden[f"conv{i}_y"])
         y.backward(torch.from_numpy(golden[f"conv{i}_gy"]).to(dev))
         for got, want in ((x.grad, golden[f"conv{i}_gx"]), (wt.grad, golden[f"conv{i}_gw"])):
@@ -304,31 +308,38 @@ def test_bounded_wait_times_out_and_reports(dev):
 
 
 @pytest.mark.parametrize("bits", [7, 8])
-def test_whole_layer_kernels_match_the_autograd_expression(dev, bits, monkeypatch):
+def test_whole_layer_kernels_match_the_reference_expression(dev, bits, monkeypatch):
     """AppConv2d with conv_impl="layer" (quantisation prologue, LUT convolution, de-quantisation epilogue and
-    their fused backward) against the same layer evaluated op by op by autograd (conv_impl="fused"): identical
-    activation codes, outputs and gradients to fp32 rounding."""
+    their fused backward) against the reference's layer expression evaluated by autograd - F.unfold + LUT-GEMM
+    for the product term, three library convolutions for the zero-point cross terms
+    (tests/reference_expression.py, after micronet+/app_layers.py:147-184): same outputs and gradients to
+    fp32 rounding."""
     import self_ops
     from lutgemm_layers import AppConv2d
+    from reference_expression import approx_conv_layer
     fp, ga_t, gb_t = O.synthetic_tables(bits, seed=40 + bits)
     self_ops.set_lookup_tables(dev, fp, ga_t, gb_t, bits)
-    # the op-by-op expression evaluates its cross terms with library convolutions: keep those in full fp32
+    # the reference expression evaluates its cross terms with library convolutions: keep those in full fp32
     monkeypatch.setattr(torch.backends.cudnn, "allow_tf32", False)
+    unfold_op = lambda a, b, **kw: self_ops.unfold_conv2d(self_ops.approx_gemm_op, a, b, **kw)
     cases = [(4, 3, 12, 12, 8, 3, 1, 1, False, False), (2, 40, 9, 11, 33, 3, 2, 1, True, True),
-             (3, 64, 8, 8, 64, 1, 2, 0, False, True), (2, 16, 10, 10, 24, 3, 1, 2, True, False)]
+             (3, 64, 8, 8, 64, 1, 2, 0, False, True), (2, 16, 10, 10, 24, 3, 1, 2, True, False),
+             (2, 8, 40, 40, 64, 3, 1, 1, False, False)]
     for s_, (B, Cin, H, W, Cout, k, st, p, bias, cl) in enumerate(cases):
         torch.manual_seed(100 * bits + s_)
-        ref = AppConv2d(Cin, Cout, k, st, p, 1, 1, bias, bits, bits, False, "fused").to(dev).train()
         new = AppConv2d(Cin, Cout, k, st, p, 1, 1, bias, bits, bits, False, "layer").to(dev).train()
-        new.load_state_dict(ref.state_dict())
         x = torch.randn(B, Cin, H, W, device=dev) * 1.5 + 0.3
         if cl:
             x = x.contiguous(memory_format=torch.channels_last)
         xr, xn = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
-        yr, yn = ref(xr), new(xn)
+        yn = new(xn)  # refreshes the layer's scales and zero points from this input, as the reference layer would
+        w_ref = new.weight.detach().clone().requires_grad_(True)
+        b_ref = new.bias.detach().clone().requires_grad_(True) if bias else None
+        yr = approx_conv_layer(unfold_op, xr, w_ref, b_ref, new.activation_scale, new.activation_zp_neg,
+                               new.weight_scale, new.weight_zp_neg, new.a_qmax, new.w_qmax, (st, st), (p, p), (1, 1))
         assert yr.shape == yn.shape
         # The output is a small difference of large terms (LUT sum against zero-point cross terms), and the
-        # library convolutions of the op-by-op expression are not exact in fp32: allow a few fp32 roundings of
+        # library convolutions of the reference expression are not exact in fp32: allow a few fp32 roundings of
         # the largest term.
         qmax = float((1 << bits) - 1)
         s_a, z_a, s_w, z_w = (float(t) for t in (new.activation_scale, new.activation_zp_neg, new.weight_scale,
@@ -350,11 +361,11 @@ def test_whole_layer_kernels_match_the_autograd_expression(dev, bits, monkeypatc
         tap = torch.nn.grad.conv2d_weight(torch.ones(1, 1, H, W, device=dev), (Cout, 1, k, k), g.sum(dim=0, keepdim=True),
                                           stride=st, padding=p)
         cross = {"x": float((s_w * z_w * box_t).abs().max()), "w": float((s_a * z_a * tap).abs().max())}
-        for a_, b_, name in ((xr.grad, xn.grad, "x"), (ref.weight.grad, new.weight.grad, "w")):
+        for a_, b_, name in ((xr.grad, xn.grad, "x"), (w_ref.grad, new.weight.grad, "w")):
             scale_ = float(a_.abs().max()) + 2.0 * cross[name]
             assert float((a_ - b_).abs().max()) <= 1e-5 * scale_ + 1e-30, (bits, s_, name)
         if bias:
-            assert torch.allclose(ref.bias.grad, new.bias.grad, rtol=1e-5, atol=1e-6)
+            assert torch.allclose(b_ref.grad, new.bias.grad, rtol=1e-5, atol=1e-6)
         assert xn.grad.stride() == xn.stride()
 
 
@@ -454,9 +465,10 @@ def test_random_shapes_through_the_dispatcher(dev, oracle_c, bits):
         assert (np.abs(gx.cpu().numpy() - r_gx) <= TOL * r_gxa + 1e-30).all(), (bits, B, Cin, H, W, Cout, k, st, p, d)
 
 
-def test_fused_straight_through_op_matches_the_unfold_one(dev, golden):
-    """approx_conv2d_fused_baseline_op against approx_conv2d_baseline_op: identical forward (the LUT sums),
-    straight-through gradients equal to fp32 rounding."""
+def test_straight_through_conv_op_matches_the_unfold_formulation(dev, golden):
+    """approx_conv2d_baseline_op (LUT convolution forward, exact-convolution gradients) against the reference's
+    formulation of it (F.unfold + LUT-GEMM forward, two matmuls backward, self_ops/ops_py/approx_ops.py:576-619):
+    identical forward (the LUT sums), straight-through gradients equal to fp32 rounding."""
     import self_ops
     bits = int(golden["bits"])
     fp, ga_t, gb_t = (O.unpack_padded(golden[k], bits) for k in ("lut_fp", "lut_ga", "lut_gb"))
@@ -465,7 +477,8 @@ def test_fused_straight_through_op_matches_the_unfold_one(dev, golden):
         B, Cin, H, W, Cout, k, s, p, d = [int(v) for v in golden[f"conv{i}_cfg"]]
         kw = dict(bias=None, stride=(s, s), padding=(p, p), dilation=(d, d), groups=1)
         outs = []
-        for op in (self_ops.approx_conv2d_baseline_op, self_ops.approx_conv2d_fused_baseline_op):
+        unfold_op = lambda a, b, **k_: self_ops.unfold_conv2d(self_ops.approx_gemm_baseline_op, a, b, **k_)
+        for op in (unfold_op, self_ops.approx_conv2d_baseline_op):
             x = torch.from_numpy(golden[f"conv{i}_x"]).to(dev).float().requires_grad_(True)
             wt = torch.from_numpy(golden[f"conv{i}_w"]).to(dev).float().requires_grad_(True)
             y = op(x, wt, **kw)
@@ -474,4 +487,4 @@ def test_fused_straight_through_op_matches_the_unfold_one(dev, golden):
         assert torch.equal(outs[0][0], outs[1][0])
         assert np.array_equal(outs[1][0].cpu().numpy(), golden[f"conv{i}_y"])
         for a_, b_ in zip(outs[0][1:], outs[1][1:]):
-            assert torch.allclose(a_, b_, rtol=2e-3, atol=1e-3 * float(a_.abs().max()))
+            assert torch.allclose(a_, b_, rtol=1e-4, atol=1e-5 * float(a_.abs().max()))
