@@ -77,6 +77,20 @@ def _load():
     lib.lutgemm_conv2d_epilogue.argtypes = [vp] * 10 + [cl, ci, ci, vp]
     lib.lutgemm_kernel_launches.restype = ctypes.c_ulonglong
     lib.lutgemm_kernel_launches.argtypes = []
+    lib.lutgemm_conv2d_forward_layer_scratch_bytes.restype = sz
+    lib.lutgemm_conv2d_forward_layer_scratch_bytes.argtypes = [ci] * 11
+    lib.lutgemm_forward_layer_scratch_bytes.restype = sz
+    lib.lutgemm_forward_layer_scratch_bytes.argtypes = [ci, ci, ci, ci]
+    lib.lutgemm_conv2d_forward_layer.restype = ci
+    lib.lutgemm_conv2d_forward_layer.argtypes = [vp, vp, vp] + [ci] * 11 + [vp] * 9 + [vp, sz, vp]
+    lib.lutgemm_forward_layer.restype = ci
+    lib.lutgemm_forward_layer.argtypes = [vp, vp, vp] + [ci] * 4 + [vp] * 9 + [vp, sz, vp]
+    lib.lutgemm_backward_f32lut_scratch_bytes.restype = sz
+    lib.lutgemm_backward_f32lut_scratch_bytes.argtypes = [ci, ci, ci, ci]
+    lib.lutgemm_backward_f32lut.restype = ci
+    lib.lutgemm_backward_f32lut.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp, sz, vp]
+    lib.lutgemm_set_handover.restype = ci
+    lib.lutgemm_set_handover.argtypes = [ci]
     lib.lutgemm_set_kernel_choice.restype = ci
     lib.lutgemm_set_kernel_choice.argtypes = [ci, ci, ci]
     lib.lutgemm_device_error.restype = ci
@@ -278,6 +292,68 @@ def approx_conv2d_forward(x: torch.Tensor, wmat: torch.Tensor, y: torch.Tensor, 
     return codes_t
 
 
+def _epilogue_args(box, sumw_t, taps, s_a, s_w, z_a, z_w, bias, M, L, Cout):
+    for t, shape, name in ((box, (M,), "box"), (sumw_t, (L, Cout), "sumw_t"), (taps, (L,), "taps")):
+        _check_input(t, torch.float32, name)
+        if tuple(t.shape) != shape:
+            raise RuntimeError(f"{name} has shape {tuple(t.shape)}, expected {shape}")
+    return [box.data_ptr(), sumw_t.data_ptr(), taps.data_ptr(), s_a.data_ptr(), s_w.data_ptr(), z_a.data_ptr(),
+            z_w.data_ptr(), bias.data_ptr() if bias is not None else None]
+
+
+def approx_conv2d_forward_layer(x: torch.Tensor, wmat: torch.Tensor, lut: torch.Tensor, kh: int, kw: int, stride: int,
+                                pad: int, dil: int, box, sumw_t, taps, s_a, s_w, z_a, z_w, bias):
+    """Whole-layer convolution forward in one kernel: the LUT sums of `approx_conv2d_forward` de-quantised as by
+    `conv2d_epilogue` while still in registers.  Returns (out f32 [B*Ho*Wo, Cout], codes_t or None)."""
+    _check_input(x, torch.uint8, "input_tensor")
+    _check_input(wmat, torch.uint8, "weight_tensor")
+    _check_input(lut, torch.uint16, "lut_appmult_tensor")
+    B, C, H, W = x.shape
+    K, Cout = wmat.shape
+    Ho, Wo = _conv_out(H, W, kh, kw, stride, pad, dil)
+    if K != C * kh * kw:
+        raise RuntimeError(f"weight_tensor's shape should be {C * kh * kw} x Cout")
+    bits = _bits_of(lut, "lut_appmult_tensor")
+    M, L = B * Ho * Wo, Ho * Wo
+    epi = _epilogue_args(box, sumw_t, taps, s_a, s_w, z_a, z_w, bias, M, L, Cout)
+    out = torch.empty((M, Cout), dtype=torch.float32, device=x.device)
+    lib = _load()
+    with torch.cuda.device(x.device):
+        ncodes = lib.lutgemm_conv2d_forward_scratch_bytes(bits, B, C, H, W, Cout, kh, kw, stride, pad, dil)
+        nbytes = lib.lutgemm_conv2d_forward_layer_scratch_bytes(bits, B, C, H, W, Cout, kh, kw, stride, pad, dil)
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=x.device) if nbytes else None
+        rc = lib.lutgemm_conv2d_forward_layer(x.data_ptr(), wmat.data_ptr(), lut.data_ptr(), bits, B, C, H, W, Cout, kh, kw,
+                                              stride, pad, dil, *epi, out.data_ptr(),
+                                              scratch.data_ptr() if nbytes else None, nbytes, _stream_ptr(x.device))
+    _check(rc, "approx_conv2d_forward_layer")
+    return out, (scratch[:ncodes] if ncodes else None)
+
+
+def approx_gemm_forward_layer(a: torch.Tensor, b: torch.Tensor, lut: torch.Tensor, box, sumw_t, taps, s_a, s_w, z_a, z_w,
+                              bias):
+    """Whole-layer linear forward in one kernel (L = 1: box [M] row sums of the codes, sumw_t [1, N], taps [1]).
+    Returns (out f32 [M, N], codes_t or None)."""
+    _check_input(a, torch.uint8, "a_tensor")
+    _check_input(b, torch.uint8, "b_tensor")
+    _check_input(lut, torch.uint16, "lut_appmult_tensor")
+    M, K = a.shape
+    N = b.shape[1]
+    if b.shape[0] != K:
+        raise RuntimeError(f"b_tensor's shape should be {K} x {N}")
+    bits = _bits_of(lut, "lut_appmult_tensor")
+    epi = _epilogue_args(box, sumw_t, taps, s_a, s_w, z_a, z_w, bias, M, 1, N)
+    out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    lib = _load()
+    with torch.cuda.device(a.device):
+        ncodes = lib.lutgemm_forward_scratch_bytes(bits, M, K, N)
+        nbytes = lib.lutgemm_forward_layer_scratch_bytes(bits, M, K, N)
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=a.device) if nbytes else None
+        rc = lib.lutgemm_forward_layer(a.data_ptr(), b.data_ptr(), lut.data_ptr(), bits, M, K, N, *epi, out.data_ptr(),
+                                       scratch.data_ptr() if nbytes else None, nbytes, _stream_ptr(a.device))
+    _check(rc, "approx_gemm_forward_layer")
+    return out, (scratch[:ncodes] if ncodes else None)
+
+
 def approx_conv2d_backward(gy: torch.Tensor, x: torch.Tensor, wmat: torch.Tensor, gx: torch.Tensor, gw: torch.Tensor,
                            lut_grad_a: torch.Tensor, lut_grad_b: torch.Tensor, kh: int, kw: int, stride: int, pad: int,
                            dil: int, codes_t: torch.Tensor = None) -> None:
@@ -322,6 +398,32 @@ def approx_conv2d_backward(gy: torch.Tensor, x: torch.Tensor, wmat: torch.Tensor
                                             stride, pad, dil, codes_t.data_ptr() if codes_t is not None else None,
                                             scratch.data_ptr(), nbytes, _stream_ptr(dev))
     _check(rc, "approx_conv2d_backward")
+
+
+def approx_gemm_backward_f32lut(gc: torch.Tensor, a: torch.Tensor, b: torch.Tensor, ga: torch.Tensor, gb: torch.Tensor,
+                                lut_grad_a: torch.Tensor, lut_grad_b: torch.Tensor) -> None:
+    """ga = sum_n gc * LUTa[a][b],  gb = sum_m LUTb[a][b] * gc with fp32 gradient tables (padded flat layout, float
+    entries, bit-widths up to 7), written in place; no 1/16 factor."""
+    for t, dt, name in ((gc, torch.float32, "gc_tensor"), (a, torch.uint8, "a_tensor"), (b, torch.uint8, "b_tensor"),
+                        (ga, torch.float32, "ga_tensor"), (gb, torch.float32, "gb_tensor"),
+                        (lut_grad_a, torch.float32, "lut_grad_a_tensor"), (lut_grad_b, torch.float32, "lut_grad_b_tensor")):
+        _check_input(t, dt, name)
+    M, K = a.shape
+    N = b.shape[1]
+    if tuple(gc.shape) != (M, N) or b.shape[0] != K or tuple(ga.shape) != (M, K) or tuple(gb.shape) != (K, N):
+        raise RuntimeError("approx_gemm_backward_f32lut: tensor shapes do not agree")
+    lib = _load()
+    bits = lib.lutgemm_bits_from_elem_num(lut_grad_a.numel())
+    if bits < 0 or bits > 7 or lut_grad_b.numel() != lut_grad_a.numel():
+        raise RuntimeError("fp32 gradient tables must both have the padded length of a bit-width up to 7")
+    dev = gc.device
+    with torch.cuda.device(dev):
+        nbytes = lib.lutgemm_backward_f32lut_scratch_bytes(bits, M, K, N)
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev) if nbytes else None
+        rc = lib.lutgemm_backward_f32lut(gc.data_ptr(), a.data_ptr(), b.data_ptr(), ga.data_ptr(), gb.data_ptr(),
+                                         lut_grad_a.data_ptr(), lut_grad_b.data_ptr(), bits, M, K, N,
+                                         scratch.data_ptr() if scratch is not None else None, nbytes, _stream_ptr(dev))
+    _check(rc, "approx_gemm_backward_f32lut")
 
 
 def _dense_4d(x: torch.Tensor, name: str) -> None:

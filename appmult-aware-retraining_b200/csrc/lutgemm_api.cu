@@ -135,6 +135,12 @@ const char *lutgemm_status_string(int status) {
     return "unknown status";
 }
 
+int lutgemm_set_handover(int on) {
+    lutgemm::slab_tall_set_handover(on != 0);
+    lutgemm::slab_fwd_set_handover(on != 0);
+    return LUTGEMM_OK;
+}
+
 unsigned long long lutgemm_kernel_launches(void) { return g_kernel_launches.load(std::memory_order_relaxed); }
 
 int lutgemm_set_kernel_choice(int forward, int backward, int grad_tile) {
@@ -174,9 +180,10 @@ static int codes_pitch(int M) { return (M + 15) & ~15; }
 // `scratch` (optional, K * codes_pitch(M) bytes, 16-byte aligned): the slab kernel then reads the activation
 // codes from a transposed copy made there first, which stays valid on return.
 static int forward_impl(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K,
-                        int N, const lutgemm::ConvGeom &conv, void *scratch, size_t scratch_bytes, void *stream) {
+                        int N, const lutgemm::ConvGeom &conv, void *scratch, size_t scratch_bytes, void *stream,
+                        const lutgemm::LayerEpilogue *epi = nullptr) {
     if (!lutgemm::bits_supported(bits)) return LUTGEMM_E_BITS;
-    if (!a || !w || !c || !lut || M <= 0 || K <= 0 || N <= 0) return LUTGEMM_E_BADARG;
+    if (!a || !w || (!c && !epi) || !lut || M <= 0 || K <= 0 || N <= 0) return LUTGEMM_E_BADARG;
     if ((reinterpret_cast<uintptr_t>(c) & 3) || (reinterpret_cast<uintptr_t>(lut) & 1) ||
         (reinterpret_cast<uintptr_t>(scratch) & 15))
         return LUTGEMM_E_BADARG;
@@ -192,9 +199,9 @@ static int forward_impl(const uint8_t *a, const uint8_t *w, uint32_t *c, const u
             if (trc != LUTGEMM_OK) return trc;
             at = static_cast<const uint8_t *>(scratch);
         }
-        return lutgemm::forward_slab(a, w, c, lut, bits, M, K, N, conv, at, pitch, sms, s);
+        return lutgemm::forward_slab(a, w, c, lut, bits, M, K, N, conv, at, pitch, epi, sms, s);
     }
-    return lutgemm::forward_rowbcast(a, w, c, lut, bits, M, K, N, conv, sms, s);
+    return lutgemm::forward_rowbcast(a, w, c, lut, bits, M, K, N, conv, epi, sms, s);
 }
 
 int lutgemm_forward(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K,
@@ -259,14 +266,14 @@ static int backward_impl(const float *gc, const uint8_t *a, const uint8_t *w, fl
             at = dst;
         }
         int rc = !pl.gw_slab ? lutgemm::backward_gw(gc, a, w, gw, lut_gw, bits, M, K, N, conv, sc, pl.gw_splits, sms, s)
-                 : pl.gw_tall ? lutgemm::backward_gw_slab_tall(gc, a, w, gw, lut_gw, bits, M, K, N, conv, sc, at, pl.gw_at_pitch, sms, s)
+                 : pl.gw_tall ? lutgemm::backward_gw_slab_tall(gc, a, w, gw, lut_gw, nullptr, bits, M, K, N, conv, sc, at, pl.gw_at_pitch, sms, s)
                              : lutgemm::backward_gw_slab_f32(gc, a, w, gw, lut_gw, bits, M, K, N, conv, sc, at, pl.gw_at_pitch, sms, s);
         if (rc != LUTGEMM_OK) return rc;
     }
     if (ga) {
         if (pl.ga_scratch && (!scratch || scratch_bytes < pl.ga_scratch)) return LUTGEMM_E_SCRATCH;
         int rc = !pl.ga_slab ? lutgemm::backward_ga(gc, a, w, ga, lut_ga, bits, M, K, N, conv, sms, s)
-                 : pl.ga_tall ? lutgemm::backward_ga_slab_tall(gc, a, w, ga, lut_ga, bits, M, K, N, conv, sc, sms, s)
+                 : pl.ga_tall ? lutgemm::backward_ga_slab_tall(gc, a, w, ga, lut_ga, nullptr, bits, M, K, N, conv, sc, sms, s)
                              : lutgemm::backward_ga_slab_f32(gc, a, w, ga, lut_ga, bits, M, K, N, conv, sc, sms, s);
         if (rc != LUTGEMM_OK) return rc;
     }
@@ -286,6 +293,44 @@ int lutgemm_backward_ws(const float *gc, const uint8_t *a, const uint8_t *w, flo
     if (reinterpret_cast<uintptr_t>(codes_t) & 15) return LUTGEMM_E_BADARG;
     lutgemm::ConvGeom none{};
     return backward_impl(gc, a, w, ga, gw, lut_ga, lut_gw, bits, M, K, N, none, codes_t, scratch, scratch_bytes, stream);
+}
+
+// ---- gradient tables in fp32 (bits <= 7) -------------------------------------------------------------------------
+// Always the tall slab kernels: their fp32 shared-memory table takes either entry type; tiles of small problems
+// are mostly empty, which costs time, not correctness.
+size_t lutgemm_backward_f32lut_scratch_bytes(int bits, int M, int K, int N) {
+    if (!lutgemm::bits_supported(bits) || bits > 7 || M <= 0 || K <= 0 || N <= 0) return 0;
+    const size_t rb_w = lutgemm::slab_tall_row_blocks(M), rb_a = lutgemm::slab_tall_row_blocks(N);
+    const size_t gw_need = rb_w > 1 ? rb_w * K * N * sizeof(float) : 0;
+    const size_t ga_need = rb_a > 1 ? rb_a * K * M * sizeof(float) : 0;
+    return gw_need > ga_need ? gw_need : ga_need;
+}
+
+int lutgemm_backward_f32lut(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, float *gw,
+                            const float *lut_ga, const float *lut_gw, int bits, int M, int K, int N, void *scratch,
+                            size_t scratch_bytes, void *stream) {
+    if (!lutgemm::bits_supported(bits) || bits > 7) return LUTGEMM_E_BITS;
+    if (!gc || !a || !w || M <= 0 || K <= 0 || N <= 0) return LUTGEMM_E_BADARG;
+    if ((ga && !lut_ga) || (gw && !lut_gw)) return LUTGEMM_E_BADARG;
+    if ((reinterpret_cast<uintptr_t>(gc) & 3) || (reinterpret_cast<uintptr_t>(ga) & 3) ||
+        (reinterpret_cast<uintptr_t>(gw) & 3) || (reinterpret_cast<uintptr_t>(scratch) & 15) ||
+        (reinterpret_cast<uintptr_t>(lut_ga) & 3) || (reinterpret_cast<uintptr_t>(lut_gw) & 3))
+        return LUTGEMM_E_BADARG;
+    if (lutgemm_backward_f32lut_scratch_bytes(bits, M, K, N) > (scratch ? scratch_bytes : 0)) return LUTGEMM_E_SCRATCH;
+    const int sms = current_num_sms();
+    if (sms <= 0) return LUTGEMM_E_CUDA;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    lutgemm::ConvGeom none{};
+    float *sc = static_cast<float *>(scratch);
+    if (gw) {
+        const int rc = lutgemm::backward_gw_slab_tall(gc, a, w, gw, nullptr, lut_gw, bits, M, K, N, none, sc, nullptr, 0, sms, s);
+        if (rc != LUTGEMM_OK) return rc;
+    }
+    if (ga) {
+        const int rc = lutgemm::backward_ga_slab_tall(gc, a, w, ga, nullptr, lut_ga, bits, M, K, N, none, sc, sms, s);
+        if (rc != LUTGEMM_OK) return rc;
+    }
+    return LUTGEMM_OK;
 }
 
 // ---- convolution entry points (implicit im2col) ------------------------------------------------------------
@@ -326,13 +371,81 @@ int lutgemm_conv2d_forward_ws(const uint8_t *x, const uint8_t *wmat, uint32_t *y
     return forward_impl(x, wmat, y, lut, bits, B * g.Ho * g.Wo, C * kh * kw, Cout, g, scratch, scratch_bytes, stream);
 }
 
+// ---- activation gradient of a convolution ------------------------------------------------------------------
+// Windows that do not overlap (kernel extent <= stride, e.g. 1x1 convolutions and patch embeddings): every image
+// position receives at most one (m,k) term, so the GEMM-shaped grad_a kernels write it in place.  Overlapping
+// windows: the pixel-mode slab kernel, one launch per stride class (lutgemm_slab_grad_tall.cu).  Either way no
+// unfolded gradient [M,K] exists.
+static bool conv_windows_overlap(const lutgemm::ConvGeom &g) {
+    return g.dil * (g.kh - 1) + 1 > g.stride || g.dil * (g.kw - 1) + 1 > g.stride;
+}
+
+// the stride class (ph, pw) of geometry g; false when the class has no pixels or no taps
+static bool make_pixel_class(const lutgemm::ConvGeom &g, int ph, int pw, lutgemm::PixelClass *px) {
+    *px = lutgemm::PixelClass{};
+    px->H = g.H; px->W = g.W; px->C = g.C; px->ph = ph; px->pw = pw; px->s = g.stride; px->Ho = g.Ho; px->Wo = g.Wo;
+    px->T = g.kh * g.kw;
+    px->Hc = ph < g.H ? (g.H - ph + g.stride - 1) / g.stride : 0;
+    px->Wc = pw < g.W ? (g.W - pw + g.stride - 1) / g.stride : 0;
+    int n = 0;
+    for (int i = 0; i < g.kh; ++i)
+        for (int j = 0; j < g.kw; ++j) {
+            const int dh = i * g.dil - g.pad, dw = j * g.dil - g.pad;
+            const int rh = (((ph - dh) % g.stride) + g.stride) % g.stride, rw = (((pw - dw) % g.stride) + g.stride) % g.stride;
+            if (rh != 0 || rw != 0) continue;
+            px->dh[n] = (int8_t)dh; px->dw[n] = (int8_t)dw; px->t[n] = (uint8_t)(i * g.kw + j);
+            ++n;
+        }
+    px->ntaps = n;
+    px->P = g.B * px->Hc * px->Wc;
+    return n > 0 && px->Hc > 0 && px->Wc > 0;
+}
+
+// pixel mode is limited by the tap tables of PixelClass
+static bool pixel_mode_supported(const lutgemm::ConvGeom &g) {
+    const int max_d = (g.kh > g.kw ? g.kh : g.kw) * g.dil;
+    return g.kh * g.kw <= lutgemm::kMaxTaps && g.kh * g.kw <= 256 && max_d <= 127 && g.pad <= 127;
+}
+
+// Per stride class: the slab kernel in pixel mode pays where its row dimension taps * Cout is long enough to
+// amortise the slab build (measured on B200: from about 4096 rows at 7 and 8 bits); otherwise, and always at 4 and
+// 6 bits where a table row is free of bank conflicts, the column-broadcast gather kernel in pixel mode.
+static bool gx_class_uses_slab(int bits, const lutgemm::PixelClass &px, int Cout) {
+    const int force = g_force_backward.load(std::memory_order_relaxed);
+    if (force == LUTGEMM_BACKWARD_BCAST) return false;
+    if (force == LUTGEMM_BACKWARD_SLAB) return true;
+    return bits >= 7 && (long)px.ntaps * Cout >= 4096;
+}
+
+static size_t conv_gx_scratch_bytes(int bits, const lutgemm::ConvGeom &g, int Cout) {
+    const int M = g.B * g.Ho * g.Wo, K = g.C * g.kh * g.kw;
+    if (!conv_windows_overlap(g)) {
+        const int sms = current_num_sms();
+        return sms > 0 ? plan_backward(bits, M, K, Cout, sms).ga_scratch : 0;
+    }
+    size_t need = 0;
+    lutgemm::PixelClass px;
+    for (int ph = 0; ph < g.stride; ++ph)
+        for (int pw = 0; pw < g.stride; ++pw)
+            if (make_pixel_class(g, ph, pw, &px) && gx_class_uses_slab(bits, px, Cout)) {
+                const size_t n = lutgemm::gx_class_scratch_bytes(bits, Cout, px, g.B);
+                need = n > need ? n : need;
+            }
+    return need;
+}
+
 size_t lutgemm_conv2d_backward_scratch_bytes(int bits, int B, int C, int H, int W, int Cout, int kh, int kw,
                                              int stride, int pad, int dil) {
     lutgemm::ConvGeom g{};
-    if (make_geom(B, C, H, W, kh, kw, stride, pad, dil, &g) != LUTGEMM_OK) return 0;
-    const size_t M = (size_t)B * g.Ho * g.Wo, K = (size_t)C * kh * kw;
-    // the unfolded activation gradient [B][K][Ho*Wo], then what the two gradient kernels need
-    return ((M * K * sizeof(float) + 15) & ~(size_t)15) + lutgemm_backward_scratch_bytes(bits, (int)M, (int)K, Cout);
+    if (!lutgemm::bits_supported(bits) || Cout <= 0 || make_geom(B, C, H, W, kh, kw, stride, pad, dil, &g) != LUTGEMM_OK)
+        return 0;
+    const int sms = current_num_sms();
+    if (sms <= 0) return 0;
+    const int M = B * g.Ho * g.Wo, K = C * kh * kw;
+    // the weight-gradient and the activation-gradient kernels run one after the other on the same buffer
+    const size_t gw_need = plan_backward(bits, M, K, Cout, sms).gw_scratch;
+    const size_t gx_need = conv_gx_scratch_bytes(bits, g, Cout);
+    return gw_need > gx_need ? gw_need : gx_need;
 }
 
 int lutgemm_conv2d_backward_ws(const float *gy, const uint8_t *x, const uint8_t *wmat, float *gx, float *gw,
@@ -343,16 +456,50 @@ int lutgemm_conv2d_backward_ws(const float *gy, const uint8_t *x, const uint8_t 
     int rc = make_geom(B, C, H, W, kh, kw, stride, pad, dil, &g);
     if (rc != LUTGEMM_OK) return rc;
     if (reinterpret_cast<uintptr_t>(codes_t) & 15) return LUTGEMM_E_BADARG;
+    if (gx && !lut_ga) return LUTGEMM_E_BADARG;
     const int M = B * g.Ho * g.Wo, K = C * kh * kw;
-    const size_t col_bytes = gx ? (((size_t)M * K * sizeof(float) + 15) & ~(size_t)15) : 0;
-    if (gx && (!scratch || scratch_bytes < col_bytes)) return LUTGEMM_E_SCRATCH;
-    float *gcol = static_cast<float *>(scratch);
-    void *rest = scratch ? static_cast<char *>(scratch) + col_bytes : nullptr;
-    const size_t rest_bytes = scratch_bytes > col_bytes ? scratch_bytes - col_bytes : 0;
-    rc = backward_impl(gy, x, wmat, gx ? gcol : nullptr, gw, lut_ga, lut_gw, bits, M, K, Cout, g, codes_t, rest,
-                       rest_bytes, stream);
-    if (rc != LUTGEMM_OK) return rc;
-    if (gx) return lutgemm::col2im_gather(gcol, gx, g, current_num_sms(), static_cast<cudaStream_t>(stream));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (gw) {
+        // first, so that under data parallelism its all-reduce can overlap the activation gradient
+        rc = backward_impl(gy, x, wmat, nullptr, gw, nullptr, lut_gw, bits, M, K, Cout, g, codes_t, scratch, scratch_bytes,
+                           stream);
+        if (rc != LUTGEMM_OK) return rc;
+    }
+    if (!gx) return LUTGEMM_OK;
+    if (!lutgemm::bits_supported(bits)) return LUTGEMM_E_BITS;
+    if (!gy || !x || !wmat || Cout <= 0) return LUTGEMM_E_BADARG;
+    if ((reinterpret_cast<uintptr_t>(gx) & 3) || (reinterpret_cast<uintptr_t>(scratch) & 15)) return LUTGEMM_E_BADARG;
+    const bool overlap = conv_windows_overlap(g);
+    const bool every_pixel_written = overlap ? stride == 1 : (stride == 1 && kh == 1 && kw == 1 && pad == 0);
+    if (!every_pixel_written &&
+        !lutgemm::cuda_ok(cudaMemsetAsync(gx, 0, (size_t)B * C * H * W * sizeof(float), s)))
+        return LUTGEMM_E_CUDA;
+    if (!overlap)  // conv.enabled makes the grad_a kernels write (m,k) to the image position it came from
+        return backward_impl(gy, x, wmat, gx, nullptr, lut_ga, nullptr, bits, M, K, Cout, g, nullptr, scratch, scratch_bytes,
+                             stream);
+    if (!pixel_mode_supported(g)) return LUTGEMM_E_TOOLARGE;
+    if (conv_gx_scratch_bytes(bits, g, Cout) > (scratch ? scratch_bytes : 0)) return LUTGEMM_E_SCRATCH;
+    const int sms = current_num_sms();
+    if (sms <= 0) return LUTGEMM_E_CUDA;
+    lutgemm::PixelClass px;
+    lutgemm::PixelClass bcast[lutgemm::kMaxClassesPerLaunch];  // classes for the broadcast kernel, launched in groups
+    int nb = 0;
+    for (int ph = 0; ph < stride; ++ph)
+        for (int pw = 0; pw < stride; ++pw) {
+            if (!make_pixel_class(g, ph, pw, &px)) continue;
+            if (gx_class_uses_slab(bits, px, Cout)) {
+                rc = lutgemm::backward_gx_class(gy, x, wmat, gx, lut_ga, bits, Cout, px, B, static_cast<float *>(scratch), sms, s);
+                if (rc != LUTGEMM_OK) return rc;
+                continue;
+            }
+            bcast[nb++] = px;
+            if (nb == lutgemm::kMaxClassesPerLaunch) {
+                rc = lutgemm::backward_gx_bcast(gy, x, wmat, gx, lut_ga, bits, Cout, bcast, nb, sms, s);
+                if (rc != LUTGEMM_OK) return rc;
+                nb = 0;
+            }
+        }
+    if (nb) return lutgemm::backward_gx_bcast(gy, x, wmat, gx, lut_ga, bits, Cout, bcast, nb, sms, s);
     return LUTGEMM_OK;
 }
 
@@ -362,6 +509,90 @@ int lutgemm_conv2d_backward(const float *gy, const uint8_t *x, const uint8_t *wm
                             size_t scratch_bytes, void *stream) {
     return lutgemm_conv2d_backward_ws(gy, x, wmat, gx, gw, lut_ga, lut_gw, bits, B, C, H, W, Cout, kh, kw, stride, pad,
                                       dil, nullptr, scratch, scratch_bytes, stream);
+}
+
+// ---- forward with the layer's de-quantisation applied where the kernel stores ------------------------------------
+static int make_epilogue(const float *box, const float *sumw_t, const float *taps, const float *s_a, const float *s_w,
+                         const float *z_a, const float *z_w, const float *bias, float *out, int L,
+                         lutgemm::LayerEpilogue *e) {
+    if (!box || !sumw_t || !taps || !s_a || !s_w || !z_a || !z_w || !out || L <= 0) return LUTGEMM_E_BADARG;
+    if (reinterpret_cast<uintptr_t>(out) & 3) return LUTGEMM_E_BADARG;
+    e->box = box; e->sumw_t = sumw_t; e->taps = taps; e->s_a = s_a; e->s_w = s_w; e->z_a = z_a; e->z_w = z_w;
+    e->bias = bias; e->out = out; e->L = L;
+    return LUTGEMM_OK;
+}
+
+// Shared body: with complete sums per tile the de-quantisation runs where the kernel stores; when cutting K across
+// CTAs fills the GPU better (few output tiles), the sums go through a uint32 buffer behind the transposed codes in
+// `scratch` and the one-pass epilogue kernel finishes them.
+static size_t align16(size_t n) { return (n + 15) & ~(size_t)15; }
+
+static bool layer_forward_needs_sums(int M, int K, int N, int sms) {
+    return forward_uses_slab(M, N) && lutgemm::slab_fwd_ksplits(M, K, N, sms) > 1;
+}
+
+static size_t layer_forward_scratch_bytes(int bits, int M, int K, int N) {
+    if (!lutgemm::bits_supported(bits) || M <= 0 || K <= 0 || N <= 0) return 0;
+    const int sms = current_num_sms();
+    if (sms <= 0) return 0;
+    const size_t codes = align16(lutgemm_forward_scratch_bytes(bits, M, K, N));
+    return codes + (layer_forward_needs_sums(M, K, N, sms) ? (size_t)M * N * sizeof(uint32_t) : 0);
+}
+
+static int layer_forward_impl(const uint8_t *a, const uint8_t *w, const uint16_t *lut, int bits, int M, int K, int N,
+                              const lutgemm::ConvGeom &conv, const lutgemm::LayerEpilogue &e, void *scratch,
+                              size_t scratch_bytes, void *stream) {
+    if (!lutgemm::bits_supported(bits)) return LUTGEMM_E_BITS;
+    if (M <= 0 || K <= 0 || N <= 0) return LUTGEMM_E_BADARG;
+    const int sms = current_num_sms();
+    if (sms <= 0) return LUTGEMM_E_CUDA;
+    const size_t codes = lutgemm_forward_scratch_bytes(bits, M, K, N);
+    if (!layer_forward_needs_sums(M, K, N, sms))
+        return forward_impl(a, w, nullptr, lut, bits, M, K, N, conv, scratch, scratch ? codes : 0, stream, &e);
+    if (!scratch || scratch_bytes < layer_forward_scratch_bytes(bits, M, K, N)) return LUTGEMM_E_SCRATCH;
+    uint32_t *sums = reinterpret_cast<uint32_t *>(static_cast<char *>(scratch) + align16(codes));
+    const int rc = forward_impl(a, w, sums, lut, bits, M, K, N, conv, scratch, codes, stream);
+    if (rc != LUTGEMM_OK) return rc;
+    return lutgemm::conv_epilogue(sums, e.box, e.sumw_t, e.taps, e.s_a, e.s_w, e.z_a, e.z_w, e.bias, e.out, M, e.L, N, sms,
+                                  static_cast<cudaStream_t>(stream));
+}
+
+size_t lutgemm_conv2d_forward_layer_scratch_bytes(int bits, int B, int C, int H, int W, int Cout, int kh, int kw,
+                                                  int stride, int pad, int dil) {
+    lutgemm::ConvGeom g{};
+    if (make_geom(B, C, H, W, kh, kw, stride, pad, dil, &g) != LUTGEMM_OK) return 0;
+    return layer_forward_scratch_bytes(bits, B * g.Ho * g.Wo, C * kh * kw, Cout);
+}
+
+size_t lutgemm_forward_layer_scratch_bytes(int bits, int M, int K, int N) {
+    return layer_forward_scratch_bytes(bits, M, K, N);
+}
+
+int lutgemm_conv2d_forward_layer(const uint8_t *x, const uint8_t *wmat, const uint16_t *lut, int bits, int B, int C, int H,
+                                 int W, int Cout, int kh, int kw, int stride, int pad, int dil, const float *box,
+                                 const float *sumw_t, const float *taps, const float *s_a, const float *s_w,
+                                 const float *z_a, const float *z_w, const float *bias, float *out, void *scratch,
+                                 size_t scratch_bytes, void *stream) {
+    lutgemm::ConvGeom g{};
+    int rc = make_geom(B, C, H, W, kh, kw, stride, pad, dil, &g);
+    if (rc != LUTGEMM_OK) return rc;
+    if (!x || !wmat || !lut || Cout <= 0) return LUTGEMM_E_BADARG;
+    lutgemm::LayerEpilogue e{};
+    rc = make_epilogue(box, sumw_t, taps, s_a, s_w, z_a, z_w, bias, out, g.Ho * g.Wo, &e);
+    if (rc != LUTGEMM_OK) return rc;
+    return layer_forward_impl(x, wmat, lut, bits, B * g.Ho * g.Wo, C * kh * kw, Cout, g, e, scratch, scratch_bytes, stream);
+}
+
+int lutgemm_forward_layer(const uint8_t *a, const uint8_t *w, const uint16_t *lut, int bits, int M, int K, int N,
+                          const float *box, const float *sumw_t, const float *taps, const float *s_a, const float *s_w,
+                          const float *z_a, const float *z_w, const float *bias, float *out, void *scratch,
+                          size_t scratch_bytes, void *stream) {
+    if (!a || !w || !lut) return LUTGEMM_E_BADARG;
+    lutgemm::ConvGeom none{};
+    lutgemm::LayerEpilogue e{};
+    const int rc = make_epilogue(box, sumw_t, taps, s_a, s_w, z_a, z_w, bias, out, 1, &e);
+    if (rc != LUTGEMM_OK) return rc;
+    return layer_forward_impl(a, w, lut, bits, M, K, N, none, e, scratch, scratch_bytes, stream);
 }
 
 // ---- layer prologue / epilogue ---------------------------------------------------------------------------

@@ -13,7 +13,14 @@
 //       warp-uniform, table staged as [a][w].  The reduction over M (262144 rows for the CIFAR
 //       convolutions, against a 576x64 output) is split into slabs across CTAs; partial sums go to a
 //       scratch buffer and a second kernel adds the slabs in ascending order (deterministic).
-// Replaces ApproxGemmBackwardKernelForGA / ForGB, self_ops/src/approx_gemm_backward.cu:13-258,261-492.
+// grad_x (PIX instantiation of the gA kernel): the activation gradient of a convolution per INPUT PIXEL.  A thread
+// owns C pixels of one stride class and R input channels; the "n" loop runs over (tap, n): for tap (i,j) the
+// grad_out rows are those of the output positions the tap connects the pixels to (zero rows where it leaves the
+// output), the weight rows are (channel, tap).  The activation code of a pixel is the same for every tap, so
+// the accumulators collect the whole sum over taps and output channels and are stored straight into
+// gx[B,C,H,W]: no unfolded gradient, no col2im.
+// Replaces ApproxGemmBackwardKernelForGA / ForGB, self_ops/src/approx_gemm_backward.cu:13-258,261-492, and for
+// grad_x the unfold backward of self_ops/ops_py/approx_ops.py:556-571.
 #include "lutgemm_common.cuh"
 #include "lutgemm_kernels.h"
 
@@ -33,14 +40,19 @@ struct GaCfg {
     static constexpr int LUT_BYTES = Q * Q * 2;
     static constexpr int G_STAGE = MT * GSTRIDE;
     static constexpr int W_STAGE = KT * NT;
-    static constexpr int SMEM = LUT_BYTES + 2 * (G_STAGE + W_STAGE);
+    static constexpr int OFF_ROWINFO = LUT_BYTES + 2 * (G_STAGE + W_STAGE);
+    static constexpr int SMEM = OFF_ROWINFO;
+    static constexpr int SMEM_PIX = OFF_ROWINFO + MT * 16;  // grad_x: {first output row, hh, ww} per pixel of the tile
 };
 
-template <int BITS, int R, int C, int WM, int WK>
+// PIX: grad_x per input pixel of the stride classes in `set` (tiles_m counts the pixel tiles of all of them, K =
+// channels, a = the code image, w = the weight matrix [C*T, N], gc = grad_out [B*Ho*Wo, N], ga = gx[B,C,H,W]).
+template <int BITS, int R, int C, int WM, int WK, bool PIX>
 __global__ void __launch_bounds__(32 * WM * WK, WM * WK <= 8 ? (C <= 2 ? 4 : 2) : 1)
 ga_colbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, const uint8_t *__restrict__ w,
                    float *__restrict__ ga, const int16_t *__restrict__ lut, int M, int K, int N, int tiles_m,
-                   int tiles_k, int vec_g, int vec_w, int vec_o, const ConvGeom conv) {
+                   int tiles_k, int vec_g, int vec_w, int vec_o, const ConvGeom conv,
+                   const __grid_constant__ PixelClassSet set) {
     using Cfg = GaCfg<BITS, R, C, WM, WK>;
     constexpr int MT = Cfg::MT, KT = Cfg::KT, NT = Cfg::NT, GS = Cfg::GSTRIDE, THREADS = Cfg::THREADS;
     constexpr uint32_t MASK = Cfg::Q - 1, MASK4 = MASK * 0x01010101u;
@@ -57,8 +69,50 @@ ga_colbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, 
     stage_table<BITS, true>(lut_s, lut, tid, THREADS);
     const uint32_t lut_addr = smem_u32(lut_s);
     const int nnt = (N + NT - 1) / NT;
+    int4 *rowinfo = reinterpret_cast<int4 *>(smem + Cfg::OFF_ROWINFO);  // PIX only
+    const PixelClass *pxp = &set.c[0];                                     // PIX only: the class of the current tile
+
+    // PIX: step = (tap q, n tile): grad_out rows of the output positions tap q connects the tile's pixels to
+    auto load_tile_pix = [&](int m0, int k0, int step, int buf) {
+        const PixelClass &px = *pxp;
+        uint8_t *gs = g_s + buf * Cfg::G_STAGE;
+        uint8_t *ws = w_s + buf * Cfg::W_STAGE;
+        const int q = step / nnt, nbase = (step - q * nnt) * NT;
+        // pixel (hh, ww) of the class sits at h = ph + s*hh; tap q reaches output row (h - dh)/s = hh + eh
+        const int eh = (px.ph - px.dh[q]) / px.s, ew = (px.pw - px.dw[q]) / px.s;
+        const int moff = eh * px.Wo + ew;
+        for (int id = tid; id < MT * (NT / 4); id += THREADS) {
+            const int r = id / (NT / 4), nc = (id % (NT / 4)) * 4;
+            const int4 info = rowinfo[r];  // {m of tap offset 0, hh, ww, valid}
+            const int oh = info.y + eh, ow = info.z + ew, gn = nbase + nc;
+            float *dst = reinterpret_cast<float *>(gs + r * GS + nc * 4);
+            const bool ok = info.w && (unsigned)oh < (unsigned)px.Ho && (unsigned)ow < (unsigned)px.Wo && gn < N;
+            const float *src = gc + (size_t)(info.x + moff) * N + gn;
+            if (ok && vec_g) cp_async16(dst, src);
+            else if (ok) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) dst[e] = gn + e < N ? src[e] : 0.f;
+            } else *reinterpret_cast<float4 *>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        const int t = px.t[q];
+        if (vec_w) {
+            for (int id = tid; id < KT; id += THREADS) {
+                const int gk = k0 + id;
+                if (gk < K && nbase < N) cp_async16(ws + id * NT, w + ((size_t)gk * px.T + t) * N + nbase);
+                else *reinterpret_cast<uint4 *>(ws + id * NT) = make_uint4(0, 0, 0, 0);
+            }
+        } else {
+            for (int id = tid; id < KT * NT; id += THREADS) {
+                const int kk = id / NT, nn = id % NT;
+                const int gk = k0 + kk, gn = nbase + nn;
+                ws[id] = (gk < K && gn < N) ? w[((size_t)gk * px.T + t) * N + gn] : (uint8_t)0;
+            }
+        }
+        cp_async_commit();
+    };
 
     auto load_tile = [&](int m0, int k0, int nt, int buf) {
+        if (PIX) { load_tile_pix(m0, k0, nt, buf); return; }
         uint8_t *gs = g_s + buf * Cfg::G_STAGE;
         uint8_t *ws = w_s + buf * Cfg::W_STAGE;
         const int nbase = nt * NT;
@@ -93,7 +147,17 @@ ga_colbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, 
     };
 
     for (int tile = blockIdx.x; tile < tiles_m * tiles_k; tile += gridDim.x) {
-        const int m0 = (tile / tiles_k) * MT, k0 = (tile % tiles_k) * KT;
+        int m0 = (tile / tiles_k) * MT;
+        const int k0 = (tile % tiles_k) * KT;
+        if (PIX) {
+            const int tm = tile / tiles_k;
+            int ci = 0;
+            while (ci + 1 < set.n && tm >= set.tile_begin[ci + 1]) ++ci;
+            pxp = &set.c[ci];
+            m0 = (tm - set.tile_begin[ci]) * MT;
+            M = pxp->P;
+        }
+        const PixelClass &px = *pxp;
         const int kth = k0 + wk * R;           // first k of this thread
         const int mth = m0 + wm * 32 * C + lane;  // first m of this thread; rows mth + 32*j
 
@@ -106,7 +170,14 @@ ga_colbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, 
             const int m = mth + 32 * j;
 #pragma unroll
             for (int q = 0; q < R / 4; ++q) acode[q][j] = 0u;
-            if (m < M) {
+            if (m < M && PIX) {
+                // the pixel's code in channels kth .. kth+R-1 (planes H*W apart)
+                const uint8_t *src = a + pixel_class_offset(px, m);
+                const size_t plane = (size_t)px.H * px.W;
+#pragma unroll
+                for (int i = 0; i < R; ++i)
+                    if (kth + i < K) acode[i >> 2][j] |= ((uint32_t)src[(kth + i) * plane] & MASK) << (8 * (i & 3));
+            } else if (m < M) {
                 if (conv.enabled) {
                     const uint4 t = conv_code16(a, conv, m, kth, K);
                     const uint32_t tw[4] = {t.x, t.y, t.z, t.w};
@@ -122,11 +193,25 @@ ga_colbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, 
             for (int i = 0; i < R; ++i) acc[i][j] = 0.f;
         }
 
+        if (PIX) {
+            // where the tile's pixels sit: output row index for tap offset 0 and the class coordinates
+            for (int r = tid; r < MT; r += THREADS) {
+                const int pm = m0 + r;
+                int4 info = make_int4(0, 0, 0, 0);
+                if (pm < M) {
+                    const int per = px.Hc * px.Wc, b = pm / per, rr = pm - b * per, hh = rr / px.Wc, ww = rr - hh * px.Wc;
+                    info = make_int4((b * px.Ho + hh) * px.Wo + ww, hh, ww, 1);
+                }
+                rowinfo[r] = info;
+            }
+            __syncthreads();
+        }
+        const int nsteps = PIX ? px.ntaps * nnt : nnt;
         load_tile(m0, k0, 0, 0);
-        for (int nt = 0; nt < nnt; ++nt) {
+        for (int nt = 0; nt < nsteps; ++nt) {
             cp_async_wait<0>();
             __syncthreads();
-            if (nt + 1 < nnt) load_tile(m0, k0, nt + 1, (nt + 1) & 1);
+            if (nt + 1 < nsteps) load_tile(m0, k0, nt + 1, (nt + 1) & 1);
             const uint8_t *gs = g_s + (nt & 1) * Cfg::G_STAGE + (wm * 32 * C + lane) * GS;
             const uint8_t *ws = w_s + (nt & 1) * Cfg::W_STAGE + (wk * R) * NT;
 #pragma unroll 1
@@ -156,14 +241,23 @@ ga_colbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, 
         for (int j = 0; j < C; ++j) {
             const int m = mth + 32 * j;
             if (m >= M) continue;
-            if (conv.enabled) {
-                // [B][K][L] layout (what col2im consumes): consecutive lanes are consecutive l, so each of
-                // these scalar stores is coalesced across the warp
-                const int L = conv.Ho * conv.Wo, b = m / L;
-                float *obase = ga + ((size_t)b * K + kth) * L + (m - b * L);
+            if (PIX) {
+                float *obase = ga + pixel_class_offset(px, m);
+                const size_t plane = (size_t)px.H * px.W;
 #pragma unroll
                 for (int i = 0; i < R; ++i)
-                    if (kth + i < K) obase[(size_t)i * L] = acc[i][j] * kGradFactor;
+                    if (kth + i < K) obase[(kth + i) * plane] = acc[i][j] * kGradFactor;
+                continue;
+            }
+            if (conv.enabled) {
+                // a convolution whose windows do not overlap: (m,k) goes straight to the image position it was
+                // read from (consecutive lanes are consecutive output positions)
+#pragma unroll
+                for (int i = 0; i < R; ++i) {
+                    if (kth + i >= K) continue;
+                    const long o = conv_scatter_index(conv, m, kth + i);
+                    if (o >= 0) ga[o] = acc[i][j] * kGradFactor;
+                }
                 continue;
             }
             float *orow = ga + (size_t)m * K + kth;
@@ -184,25 +278,27 @@ ga_colbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, 
     }
 }
 
-template <int BITS, int R, int C, int WM, int WK>
+template <int BITS, int R, int C, int WM, int WK, bool PIX = false>
 static int launch_ga(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, const int16_t *lut, int M,
-                     int K, int N, const ConvGeom &conv, int num_sms, cudaStream_t stream) {
+                     int K, int N, const ConvGeom &conv, int num_sms, cudaStream_t stream,
+                     const PixelClassSet *set = nullptr) {
     using Cfg = GaCfg<BITS, R, C, WM, WK>;
-    auto kern = ga_colbcast_kernel<BITS, R, C, WM, WK>;
-    if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM)))
+    auto kern = ga_colbcast_kernel<BITS, R, C, WM, WK, PIX>;
+    constexpr int SMEM = PIX ? Cfg::SMEM_PIX : Cfg::SMEM;
+    if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM)))
         return LUTGEMM_E_CUDA;
-    const int tiles_m = (M + Cfg::MT - 1) / Cfg::MT, tiles_k = (K + Cfg::KT - 1) / Cfg::KT;
+    const int tiles_m = PIX ? set->tile_begin[set->n] : (M + Cfg::MT - 1) / Cfg::MT, tiles_k = (K + Cfg::KT - 1) / Cfg::KT;
     const long tiles = (long)tiles_m * tiles_k;
     int ctas_per_sm = 1;  // persistent grid: as many CTAs as the SMs hold at once
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, kern, Cfg::THREADS, Cfg::SMEM) != cudaSuccess ||
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, kern, Cfg::THREADS, SMEM) != cudaSuccess ||
         ctas_per_sm < 1)
         ctas_per_sm = 1;
     const int grid = (int)(tiles < (long)num_sms * ctas_per_sm ? tiles : (long)num_sms * ctas_per_sm);
     const int vec_g = (N % 4 == 0) && ((reinterpret_cast<uintptr_t>(gc) & 15) == 0);
     const int vec_w = (N % 16 == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
     const int vec_o = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(ga) & 15) == 0);
-    kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(gc, a, w, ga, lut, M, K, N, tiles_m, tiles_k, vec_g, vec_w, vec_o,
-                                                    conv);
+    kern<<<grid, Cfg::THREADS, SMEM, stream>>>(gc, a, w, ga, lut, M, K, N, tiles_m, tiles_k, vec_g, vec_w, vec_o, conv,
+                                               set ? *set : PixelClassSet{});
     return launch_status();
 }
 
@@ -216,6 +312,36 @@ int backward_ga(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, 
         case 7: return launch_ga<7, 8, 4, 2, 4>(gc, a, w, ga, lut_ga, M, K, N, conv, num_sms, stream);
         // the 128 KB table leaves room for one CTA per SM only: make it 16 warps
         case 8: return launch_ga<8, 8, 4, 4, 4>(gc, a, w, ga, lut_ga, M, K, N, conv, num_sms, stream);
+    }
+    return LUTGEMM_E_BITS;
+}
+
+template <int BITS, int R, int C, int WM, int WK>
+static int launch_gx_bcast(const float *gy, const uint8_t *x, const uint8_t *wmat, float *gx, const int16_t *lut_ga,
+                           int Cout, const PixelClass *classes, int nclasses, int num_sms, cudaStream_t stream) {
+    constexpr int MT = GaCfg<BITS, R, C, WM, WK>::MT;
+    ConvGeom none{};
+    for (int first = 0; first < nclasses; first += kMaxClassesPerLaunch) {
+        PixelClassSet set{};
+        set.n = nclasses - first < kMaxClassesPerLaunch ? nclasses - first : kMaxClassesPerLaunch;
+        for (int i = 0; i < set.n; ++i) {
+            set.c[i] = classes[first + i];
+            set.tile_begin[i + 1] = set.tile_begin[i] + (set.c[i].P + MT - 1) / MT;
+        }
+        const int rc = launch_ga<BITS, R, C, WM, WK, true>(gy, x, wmat, gx, lut_ga, 0, classes[first].C, Cout, none, num_sms,
+                                                           stream, &set);
+        if (rc != LUTGEMM_OK) return rc;
+    }
+    return LUTGEMM_OK;
+}
+
+int backward_gx_bcast(const float *gy, const uint8_t *x, const uint8_t *wmat, float *gx, const int16_t *lut_ga, int bits,
+                      int Cout, const PixelClass *classes, int nclasses, int num_sms, cudaStream_t stream) {
+    switch (bits) {
+        case 4: return launch_gx_bcast<4, 8, 4, 2, 4>(gy, x, wmat, gx, lut_ga, Cout, classes, nclasses, num_sms, stream);
+        case 6: return launch_gx_bcast<6, 8, 4, 2, 4>(gy, x, wmat, gx, lut_ga, Cout, classes, nclasses, num_sms, stream);
+        case 7: return launch_gx_bcast<7, 8, 4, 2, 4>(gy, x, wmat, gx, lut_ga, Cout, classes, nclasses, num_sms, stream);
+        case 8: return launch_gx_bcast<8, 8, 4, 4, 4>(gy, x, wmat, gx, lut_ga, Cout, classes, nclasses, num_sms, stream);
     }
     return LUTGEMM_E_BITS;
 }
@@ -453,64 +579,6 @@ int backward_gw(const float *gc, const uint8_t *a, const uint8_t *w, float *gw, 
     return LUTGEMM_E_BITS;
 }
 
-// ------------------------------------------------------------------------------------------------
-// col2im: gx[b,c,h,w] = sum over the taps (i, j) that reach (h, w) of gcol[b][(c*kh+i)*kw+j][oh*Wo+ow].
-// A gather (one thread per input pixel, taps in ascending (i, j) order), so the fp32 sum order is fixed;
-// consecutive threads read consecutive ow of the same gcol row.  Adjoint of the implicit im2col above
-// (the reference gets it from autograd of F.unfold / F.pad, self_ops/ops_py/approx_ops.py:556-563).
-// ------------------------------------------------------------------------------------------------
-template <bool STRIDE1>
-__global__ void __launch_bounds__(256) col2im_gather_kernel(const float *__restrict__ gcol, float *__restrict__ gx,
-                                                            const ConvGeom g) {
-    // one thread per four consecutive w of an input row (b, c, h)
-    const int W4 = (g.W + 3) / 4;
-    const long total = (long)g.B * g.C * g.H * W4;
-    const int L = g.Ho * g.Wo, K = g.C * g.kh * g.kw;
-    for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
-        const int w0 = (int)(idx % W4) * 4;
-        const long row_id = idx / W4;           // (b * C + c) * H + h
-        const int h = (int)(row_id % g.H);
-        const int bc = (int)(row_id / g.H);
-        const int c = bc % g.C, b = bc / g.C;
-        const float *base = gcol + ((size_t)b * K + (size_t)c * g.kh * g.kw) * L;
-        float s[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int i = 0; i < g.kh; ++i) {
-            const int th = h + g.pad - i * g.dil;
-            if (th < 0) continue;
-            int oh = th;
-            if (!STRIDE1) {
-                if (th % g.stride) continue;
-                oh = th / g.stride;
-            }
-            if (oh >= g.Ho) continue;
-            const float *row = base + (size_t)(i * g.kw) * L + (size_t)oh * g.Wo;
-            for (int j = 0; j < g.kw; ++j) {
-                const float *rj = row + (size_t)j * L;
-                const int tw0 = w0 + g.pad - j * g.dil;
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int tw = tw0 + e;
-                    int ow = tw;
-                    bool ok = tw >= 0 && w0 + e < g.W;
-                    if (!STRIDE1) {
-                        ok = ok && (tw % g.stride == 0);
-                        ow = tw / g.stride;
-                    }
-                    if (ok && ow < g.Wo) s[e] += rj[ow];
-                }
-            }
-        }
-        float *dst = gx + row_id * g.W + w0;
-        if (w0 + 3 < g.W && (g.W & 3) == 0 && (reinterpret_cast<uintptr_t>(gx) & 15) == 0) {
-            *reinterpret_cast<float4 *>(dst) = make_float4(s[0], s[1], s[2], s[3]);
-        } else {
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-                if (w0 + e < g.W) dst[e] = s[e];
-        }
-    }
-}
-
 // at[k][m..m+15] per thread: lanes run over m, so the 16-byte stores are coalesced.  For the unfolded code
 // image the (channel, tap) of k and the (image, row, column) of the first m are decoded once per thread and m
 // advances incrementally; for a plain [M,K] matrix the byte loads of the 32 k of a block share sectors.
@@ -590,16 +658,6 @@ int transpose_codes(const uint8_t *a, uint8_t *at, int M, int K, int pitch, cons
     const dim3 block(32, 32), grid((pitch / 16 + 31) / 32, (K + 31) / 32);
     if (grid.y > 65535u) return LUTGEMM_E_TOOLARGE;
     transpose_codes_kernel<<<grid, block, 0, stream>>>(a, at, M, K, pitch, conv);
-    return launch_status();
-}
-
-int col2im_gather(const float *gcol, float *gx, const ConvGeom &g, int num_sms, cudaStream_t stream) {
-    const long total = (long)g.B * g.C * g.H * ((g.W + 3) / 4);
-    const long blocks = (total + 255) / 256;
-    const long cap = (long)num_sms * 32;
-    const int grid = (int)(blocks < cap ? blocks : cap);
-    if (g.stride == 1) col2im_gather_kernel<true><<<grid, 256, 0, stream>>>(gcol, gx, g);
-    else col2im_gather_kernel<false><<<grid, 256, 0, stream>>>(gcol, gx, g);
     return launch_status();
 }
 

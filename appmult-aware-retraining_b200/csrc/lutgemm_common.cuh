@@ -59,6 +59,79 @@ __device__ __forceinline__ uint4 conv_code16(const uint8_t *__restrict__ x, cons
     return make_uint4(t[0], t[1], t[2], t[3]);
 }
 
+// Where grad_a[m,k] of a convolution lands in the image gradient gx[B,C,H,W] when the kernel windows do not
+// overlap (every image position is touched by at most one (m,k)): the position a[m,k] was read from, or -1
+// for padding.  Used by the gradient kernels to write such convolutions' activation gradient in place.
+__device__ __forceinline__ long conv_scatter_index(const ConvGeom &g, int m, int k) {
+    const int L = g.Ho * g.Wo, kk = g.kh * g.kw;
+    const int b = m / L, l = m - b * L, oh = l / g.Wo, ow = l - oh * g.Wo;
+    const int c = k / kk, r = k - c * kk, i = r / g.kw, j = r - i * g.kw;
+    const int ih = oh * g.stride - g.pad + i * g.dil, iw = ow * g.stride - g.pad + j * g.dil;
+    if ((unsigned)ih < (unsigned)g.H && (unsigned)iw < (unsigned)g.W)
+        return (((long)b * g.C + c) * g.H + ih) * g.W + iw;
+    return -1;
+}
+
+// Input pixels of one stride class of a convolution - h = ph + s*hh, w = pw + s*ww - and the kernel taps that
+// reach them.  The activation gradient of an input pixel sums, over those taps (i,j) and the output channels n,
+// gy[(b, (h - dh)/s, (w - dw)/s), n] * T(x[b,c,h,w], wmat[(c*T + t), n])  with dh = i*dil - pad, t = i*kw + j.
+constexpr int kMaxTaps = 128;
+struct PixelClass {
+    int H, W, C;            // image
+    int Hc, Wc;             // pixels of the class per image
+    int ph, pw, s;
+    int Ho, Wo;             // output positions of the convolution
+    int ntaps, T;           // taps of the class; kh*kw
+    int P;                  // pixels of the class over all images: B * Hc * Wc
+    int8_t dh[kMaxTaps], dw[kMaxTaps];
+    uint8_t t[kMaxTaps];
+};
+// up to four classes handled by one launch (all classes of a stride-2 convolution): class i owns the pixel tiles
+// [tile_begin[i], tile_begin[i+1])
+constexpr int kMaxClassesPerLaunch = 4;
+struct PixelClassSet {
+    int n;
+    int tile_begin[kMaxClassesPerLaunch + 1];
+    PixelClass c[kMaxClassesPerLaunch];
+};
+// pixel p of the class (counted over all images) -> offset of (b, channel 0, h, w) in the NCHW image
+__host__ __device__ __forceinline__ size_t pixel_class_offset(const PixelClass &px, int p) {
+    const int per = px.Hc * px.Wc, b = p / per, r = p - b * per, hh = r / px.Wc, ww = r - hh * px.Wc;
+    return (size_t)b * px.C * px.H * px.W + (size_t)(px.ph + px.s * hh) * px.W + (px.pw + px.s * ww);
+}
+
+// De-quantisation of an approximate layer applied where a forward kernel stores its sums (out != nullptr):
+//   out[m,n] = s_a s_w (sum[m,n] + z_w box[m] + z_a sumw_t[l,n] + z_a z_w taps[l]) (+ bias[n]),   l = m mod L
+// every product and sum rounded separately in this order (the order the layer expression of
+// micronet+/app_layers.py:175-184 evaluates them).  All scalars are device pointers: nothing syncs with the host.
+struct LayerEpilogue {
+    const float *box, *sumw_t, *taps, *s_a, *s_w, *z_a, *z_w, *bias;
+    float *out;
+    int L;
+};
+struct LayerEpilogueScalars {
+    float s, za, zw, zz;
+};
+__device__ __forceinline__ LayerEpilogueScalars load_epilogue_scalars(const LayerEpilogue &e) {
+    LayerEpilogueScalars v;
+    v.za = *e.z_a;
+    v.zw = *e.z_w;
+    v.s = __fmul_rn(*e.s_a, *e.s_w);
+    v.zz = __fmul_rn(v.za, v.zw);
+    return v;
+}
+// row terms: z_w box[m] and z_a z_w taps[l], shared by every column of the row
+__device__ __forceinline__ float epilogue_value(const LayerEpilogue &e, const LayerEpilogueScalars &v, uint32_t sum,
+                                                float zw_box, float zz_taps, int l, int n, int N) {
+    float acc = (float)sum;
+    acc = __fadd_rn(acc, zw_box);
+    acc = __fadd_rn(acc, __fmul_rn(v.za, e.sumw_t[(size_t)l * N + n]));
+    acc = __fadd_rn(acc, zz_taps);
+    float o = __fmul_rn(v.s, acc);
+    if (e.bias) o = __fadd_rn(o, e.bias[n]);
+    return o;
+}
+
 // ---- small device helpers ----------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

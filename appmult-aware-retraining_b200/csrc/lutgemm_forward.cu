@@ -31,7 +31,7 @@ template <int BITS, int R, int C, int WM, int WN>
 __global__ void __launch_bounds__(32 * WM * WN, 1)
 fwd_rowbcast_kernel(const uint8_t *__restrict__ a, const uint8_t *__restrict__ w, uint32_t *__restrict__ c,
                     const uint16_t *__restrict__ lut, int M, int K, int N, int tiles_m, int tiles_n,
-                    int vec_a, int vec_w, int vec_c, const ConvGeom conv) {
+                    int vec_a, int vec_w, int vec_c, const ConvGeom conv, const LayerEpilogue epi) {
     using Cfg = FwdCfg<BITS, R, C, WM, WN>;
     constexpr int KT = Cfg::KT, MT = Cfg::MT, NT = Cfg::NT, THREADS = Cfg::THREADS;
     constexpr uint32_t MASK = Cfg::Q - 1;
@@ -159,10 +159,22 @@ fwd_rowbcast_kernel(const uint8_t *__restrict__ a, const uint8_t *__restrict__ w
 
         // epilogue: each lane owns C adjacent columns of R rows
         const int nbase = n0 + wn * 32 * C + lane * C;
+        LayerEpilogueScalars ev{};
+        if (epi.out) ev = load_epilogue_scalars(epi);
 #pragma unroll
         for (int i = 0; i < R; ++i) {
             const int m = m0 + wm * R + i;
             if (m >= M) continue;
+            if (epi.out) {
+                // the layer's de-quantisation applied to the sums in registers
+                const int l = m % epi.L;
+                const float zw_box = __fmul_rn(ev.zw, epi.box[m]), zz_taps = __fmul_rn(ev.zz, epi.taps[l]);
+                float *orow = epi.out + (size_t)m * N;
+#pragma unroll
+                for (int j = 0; j < C; ++j)
+                    if (nbase + j < N) orow[nbase + j] = epilogue_value(epi, ev, acc[i][j], zw_box, zz_taps, l, nbase + j, N);
+                continue;
+            }
             uint32_t *crow = c + (size_t)m * N;
             if (vec_c) {
                 if constexpr (C >= 4) {
@@ -186,7 +198,7 @@ fwd_rowbcast_kernel(const uint8_t *__restrict__ a, const uint8_t *__restrict__ w
 
 template <int BITS, int R, int C, int WM, int WN>
 static int launch_fwd(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int M, int K, int N,
-                      const ConvGeom &conv, int num_sms, cudaStream_t stream) {
+                      const ConvGeom &conv, const LayerEpilogue *epi, int num_sms, cudaStream_t stream) {
     using Cfg = FwdCfg<BITS, R, C, WM, WN>;
     auto kern = fwd_rowbcast_kernel<BITS, R, C, WM, WN>;
     if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM)))
@@ -198,24 +210,25 @@ static int launch_fwd(const uint8_t *a, const uint8_t *w, uint32_t *c, const uin
     const int vec_a = !conv.enabled && (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(a) & 15) == 0);
     const int vec_w = (N % 16 == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
     const int vec_c = (N % 4 == 0) && ((reinterpret_cast<uintptr_t>(c) & 15) == 0);
-    kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(a, w, c, lut, M, K, N, tiles_m, tiles_n, vec_a, vec_w, vec_c, conv);
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(a, w, c, lut, M, K, N, tiles_m, tiles_n, vec_a, vec_w, vec_c, conv,
+                                                    epi ? *epi : LayerEpilogue{});
     return launch_status();
 }
 
 template <int BITS>
 static int dispatch_fwd(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int M, int K, int N,
-                        const ConvGeom &conv, int num_sms, cudaStream_t stream) {
-    if (N <= 128) return launch_fwd<BITS, 16, 2, 8, 1>(a, w, c, lut, M, K, N, conv, num_sms, stream);
-    return launch_fwd<BITS, 8, 8, 8, 1>(a, w, c, lut, M, K, N, conv, num_sms, stream);
+                        const ConvGeom &conv, const LayerEpilogue *epi, int num_sms, cudaStream_t stream) {
+    if (N <= 128) return launch_fwd<BITS, 16, 2, 8, 1>(a, w, c, lut, M, K, N, conv, epi, num_sms, stream);
+    return launch_fwd<BITS, 8, 8, 8, 1>(a, w, c, lut, M, K, N, conv, epi, num_sms, stream);
 }
 
 int forward_rowbcast(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K,
-                     int N, const ConvGeom &conv, int num_sms, cudaStream_t stream) {
+                     int N, const ConvGeom &conv, const LayerEpilogue *epi, int num_sms, cudaStream_t stream) {
     switch (bits) {
-        case 4: return dispatch_fwd<4>(a, w, c, lut, M, K, N, conv, num_sms, stream);
-        case 6: return dispatch_fwd<6>(a, w, c, lut, M, K, N, conv, num_sms, stream);
-        case 7: return dispatch_fwd<7>(a, w, c, lut, M, K, N, conv, num_sms, stream);
-        case 8: return dispatch_fwd<8>(a, w, c, lut, M, K, N, conv, num_sms, stream);
+        case 4: return dispatch_fwd<4>(a, w, c, lut, M, K, N, conv, epi, num_sms, stream);
+        case 6: return dispatch_fwd<6>(a, w, c, lut, M, K, N, conv, epi, num_sms, stream);
+        case 7: return dispatch_fwd<7>(a, w, c, lut, M, K, N, conv, epi, num_sms, stream);
+        case 8: return dispatch_fwd<8>(a, w, c, lut, M, K, N, conv, epi, num_sms, stream);
     }
     return LUTGEMM_E_BITS;
 }

@@ -18,14 +18,21 @@ inline bool cuda_ok(cudaError_t e) {
 // status of the launch just made on this thread
 int launch_status();
 
-struct ConvGeom;  // lutgemm_common.cuh; geometry.enabled == 0 means `a` is a plain [M,K] matrix
+struct ConvGeom;    // lutgemm_common.cuh; geometry.enabled == 0 means `a` is a plain [M,K] matrix
+struct PixelClass;  // lutgemm_common.cuh; the input pixels of one stride class of a convolution and their taps
+struct LayerEpilogue;  // lutgemm_common.cuh; optional de-quantisation applied where the forward kernels store
 
+// `epi` (optional): the kernel stores the de-quantised fp32 layer output epi->out instead of the uint32 sums c
 int forward_rowbcast(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K,
-                     int N, const ConvGeom &conv, int num_sms, cudaStream_t stream);
+                     int N, const ConvGeom &conv, const LayerEpilogue *epi, int num_sms, cudaStream_t stream);
 
 // `at` (optional): the activation codes transposed, at[k][m] with rows at_pitch bytes apart (transpose_codes)
 int forward_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K, int N,
-                 const ConvGeom &conv, const uint8_t *at, int at_pitch, int num_sms, cudaStream_t stream);
+                 const ConvGeom &conv, const uint8_t *at, int at_pitch, const LayerEpilogue *epi, int num_sms,
+                 cudaStream_t stream);
+
+// number of K ranges forward_slab cuts a problem into when it is free to (1 = none; a fused epilogue needs 1)
+int slab_fwd_ksplits(int M, int K, int N, int num_sms);
 
 // rows of the reduction dimension per CTA tile of the fp32-slab gradient kernels, and the block count
 constexpr int kSlabF32Rows = 512;
@@ -41,27 +48,42 @@ int backward_ga_slab_f32(const float *gc, const uint8_t *a, const uint8_t *w, fl
 // the same with a tall tile (1024 rows x 32 columns): half the slab-build work per look-up
 constexpr int kSlabTallRows = 1024;
 int slab_tall_row_blocks(int rdim);
+// lut_f32 (optional, bits <= 7): the gradient table as fp32 in the same padded layout; it replaces the int16
+// table and the 1/16 scale
 int backward_gw_slab_tall(const float *gc, const uint8_t *a, const uint8_t *w, float *gw, const int16_t *lut_gw,
-                          int bits, int M, int K, int N, const ConvGeom &conv, float *scratch, const uint8_t *at,
-                          int at_pitch, int num_sms, cudaStream_t stream);
+                          const float *lut_f32, int bits, int M, int K, int N, const ConvGeom &conv, float *scratch,
+                          const uint8_t *at, int at_pitch, int num_sms, cudaStream_t stream);
 int backward_ga_slab_tall(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, const int16_t *lut_ga,
-                          int bits, int M, int K, int N, const ConvGeom &conv, float *scratch, int num_sms,
-                          cudaStream_t stream);
+                          const float *lut_f32, int bits, int M, int K, int N, const ConvGeom &conv, float *scratch,
+                          int num_sms, cudaStream_t stream);
 // reads (and clears) the device-side error word of the bounded barrier waits; synchronises the device
 int read_and_clear_device_error(int *value);
 // launches a one-warp kernel whose barrier wait can never be satisfied (it must time out with error id 99)
 int bounded_wait_selftest(cudaStream_t stream);
-// out[k][c] (or out[c][k] when transpose) = 1/16 * sum over row blocks of part[b][k][c], b ascending
-int slab_reduce_blocks(const float *part, float *out, int K, int C, int nblocks, bool transpose, int bkl_L,
-                       int num_sms, cudaStream_t stream);
+// out[k][c] (or out[c][k] when transpose) = 1/16 * sum over row blocks of part[b][k][c], b ascending; with
+// `scatter` (columns are unfolded rows of that convolution) or `px` (columns are pixels of that class, k a
+// channel) the sums go to their positions in the image gradient instead
+int slab_reduce_blocks(const float *part, float *out, int K, int C, int nblocks, bool transpose, const ConvGeom *scatter,
+                       const PixelClass *px, float scale, int num_sms, cudaStream_t stream);
+// activation gradient of a convolution for the input pixels of one stride class, written into gx[B,C,H,W]
+// (tall slab kernel in pixel mode: no unfolded gradient, no col2im); scratch: gx_class_scratch_bytes()
+size_t gx_class_scratch_bytes(int bits, int Cout, const PixelClass &px, int B);
+int backward_gx_class(const float *gy, const uint8_t *x, const uint8_t *wmat, float *gx, const int16_t *lut_ga, int bits,
+                      int Cout, const PixelClass &px, int B, float *scratch, int num_sms, cudaStream_t stream);
+// the same with the column-broadcast gather kernel (whole table in shared memory, no slab) for `nclasses` stride
+// classes at once (up to four per launch, so that small images still fill the GPU): better where the row dimension
+// taps * Cout is too short to amortise a slab build
+int backward_gx_bcast(const float *gy, const uint8_t *x, const uint8_t *wmat, float *gx, const int16_t *lut_ga, int bits,
+                      int Cout, const PixelClass *classes, int nclasses, int num_sms, cudaStream_t stream);
+// hand-over between the warps of the tall gradient / forward slab kernels: per-buffer mbarriers (default) or one
+// CTA barrier per k
+void slab_tall_set_handover(bool on);
+void slab_fwd_set_handover(bool on);
 
 
 // at[k][m] = a[m][k] (or the unfolded code image when conv.enabled); rows `pitch` bytes apart, pitch a multiple
 // of 16 and >= M, columns m >= M are written as 0
 int transpose_codes(const uint8_t *a, uint8_t *at, int M, int K, int pitch, const ConvGeom &conv, cudaStream_t stream);
-
-// gx[B,C,H,W] from the unfolded activation gradient gcol[B][C*kh*kw][Ho*Wo] (deterministic gather)
-int col2im_gather(const float *gcol, float *gx, const ConvGeom &g, int num_sms, cudaStream_t stream);
 
 // quantisation prologue / epilogue of an approximate convolution layer (lutgemm_quant.cu); strides in elements
 int quantize_codes(const float *x, long sb, long sc, long sh, long sw, int B, int C, int H, int W, const float *scale,
@@ -76,6 +98,8 @@ int conv_epilogue(const uint32_t *y, const float *box, const float *sumw_t, cons
 // number of slabs the weight-gradient kernel splits M into (1 = no scratch needed)
 int gw_num_splits(int bits, int M, int K, int N, int num_sms);
 
+// with conv.enabled (a convolution whose windows do not overlap) ga is the image gradient gx[B,C,H,W] and every
+// (m,k) is written to the position its activation came from; the caller zero-fills gx where nothing lands
 int backward_ga(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, const int16_t *lut_ga, int bits,
                 int M, int K, int N, const ConvGeom &conv, int num_sms, cudaStream_t stream);
 

@@ -14,7 +14,12 @@
 // shared-memory wavefront instead of ~11.  The build reads the table transposed and paired ([w][x],
 // codes x and x + 2^b/2 in one word) with conflict-free 32-bit loads and writes slab rows (stride 34
 // words) with conflict-free 64-bit stores: 2^b * 2 wavefronts per k against 512 for the use phase.
-// Two slab buffers: slab k+1 is built while slab k is read, one CTA barrier per k.
+// Two slab buffers: slab k+1 is built while slab k is read.  The warps hand the buffers to each other through
+// mbarriers (per buffer a "full" barrier - all 16 warps have built their part - and an "empty" barrier - all
+// have finished reading it; one arrival per warp): a warp reads half of its rows of slab k, then, once slab
+// k-1 has been released, builds its part of slab k+1 and reads the other half, so each wait has half a read
+// phase of slack and the warps drift instead of lining up behind one CTA barrier per k.  Every wait is bounded
+// (lutgemm_waits.cuh).
 // The two halves of a slab word go to the accumulators as  S += word,  H += word >> 16 ; at the end
 // sum(lo) = S - (H << 16) (mod 2^32) and sum(hi) = H.
 // Work items are (tile, K split); splits of one tile are combined with integer atomics, which are
@@ -27,6 +32,7 @@
 // Replaces ApproxGemmForwardKernel, self_ops/src/approx_gemm_forward.cu:37-229.
 #include "lutgemm_common.cuh"
 #include "lutgemm_kernels.h"
+#include "lutgemm_waits.cuh"
 
 namespace lutgemm {
 namespace sf {
@@ -45,7 +51,8 @@ struct Cfg {
     static constexpr int U_BYTES = Q * U_STRIDE * 4;
     static constexpr int RC_STAGE = KC * RT;
     static constexpr int CC_STAGE = KC * CT;
-    static constexpr int SMEM = TT_BYTES + 2 * U_BYTES + 2 * RC_STAGE + 2 * CC_STAGE;
+    static constexpr int OFF_BAR = TT_BYTES + 2 * U_BYTES + 2 * RC_STAGE + 2 * CC_STAGE;
+    static constexpr int SMEM = OFF_BAR + 4 * 8 + 16;  // four mbarriers and the abort word
     static constexpr int NSETS = HALF > 32 ? HALF / 32 : 1;
 };
 
@@ -60,11 +67,14 @@ struct Args {
     ConvGeom conv;
     const uint8_t *at;  // optional: the activation codes transposed, at[k][m], rows at_pitch bytes apart
     int at_pitch;       // a multiple of 16; columns m >= M hold 0
+    int *error_word;    // device error word of the bounded waits
+    LayerEpilogue epi;  // epi.out != nullptr: the de-quantised fp32 layer output is stored instead of c
 };
 
 // USE_AT: the activation codes come from the transposed workspace copy (p.at); the other instantiation keeps
 // the direct / implicit-im2col fetch, so neither carries the other's registers.
-template <int BITS, bool USE_AT>
+// HANDOVER: per-buffer mbarriers (see the file comment) instead of one CTA barrier per k.
+template <int BITS, bool USE_AT, bool HANDOVER>
 __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p) {
     using C = Cfg<BITS>;
     constexpr int Q = C::Q, HALF = C::HALF, TTS = C::TT_STRIDE, RT = C::RT, CT = C::CT, KC = C::KC;
@@ -78,7 +88,10 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p) {
     uint8_t *cc_s = rc_s + 2 * C::RC_STAGE;
     const uint32_t tt_addr = smem_u32(smem);
     const uint32_t u_addr = smem_u32(smem + C::TT_BYTES);
+    const uint32_t bar_full = smem_u32(smem + C::OFF_BAR), bar_empty = bar_full + 16;
+    volatile int *abort_word = reinterpret_cast<volatile int *>(smem + C::OFF_BAR + 32);
     const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
+    if (tid == 0) *abort_word = 0;
 
     // ---- stage the table transposed and paired: tt[w][i] = { LUT[i][w], LUT[i + HALF][w] } ---------------
     {
@@ -155,6 +168,7 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p) {
     };
 
     const int items = p.tiles_r * p.tiles_c * p.ksplits;
+    bool first_item = true;
     for (int item = blockIdx.x; item < items; item += gridDim.x) {
         const int tile = item / p.ksplits;
         const int kbeg = (item % p.ksplits) * p.k_per_split, kend = min(K, kbeg + p.k_per_split);
@@ -167,40 +181,92 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p) {
         fetch_chunk(m0, n0, kbeg / KC);
         __syncthreads();  // previous item (or the table staging) is done with every buffer
         store_chunk((kbeg / KC) & 1);
+        if (HANDOVER && tid == 0) {
+            // fresh barriers for this item: phases restart at 0 (nobody is waiting or arriving here)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                if (!first_item) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar_full + 8 * b) : "memory");
+                mbar_init(bar_full + 8 * b, 16);
+            }
+        }
+        first_item = false;
         __syncthreads();
         build(kbeg & 1, (kbeg / KC) & 1, 0);
-        __syncthreads();
+        if (HANDOVER) {
+            __syncwarp();
+            // slab kbeg is complete once every warp has arrived; the other buffer starts out released
+            if (lane == 0) {
+                mbar_arrive(bar_full + 8 * (kbeg & 1));
+                mbar_arrive(bar_empty + 8 * ((kbeg & 1) ^ 1));
+            }
+        } else {
+            __syncthreads();
+        }
 
-        for (int k = kbeg; k < kend; ++k) {
-            const int chunk = k / KC, kk = k % KC, stage = chunk & 1;
-            const bool have_next_chunk = (chunk + 1) * KC < kend;
-            if (kk == 0 && have_next_chunk) fetch_chunk(m0, n0, chunk + 1);
-            if (k + 1 < kend) build((k + 1) & 1, ((k + 1) / KC) & 1, (k + 1) % KC);
-
-            // use slab k: slab row a[m,k], two columns per lane, for this warp's 32 rows
+        // use slab k: slab row a[m,k], two columns per lane, for rows [rb, re) of this warp's 32 rows
+        auto use_rows = [&](int k, int stage, int kk, int rb, int re) {
             const uint4 *rp = reinterpret_cast<const uint4 *>(rc_s + stage * C::RC_STAGE + kk * RT + wp * 32);
-            const uint4 q0 = rp[0], q1 = rp[1];
-            const uint32_t rv[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+            const uint4 q0 = rp[rb / 16];
+            const uint32_t rv[4] = {q0.x, q0.y, q0.z, q0.w};
             const uint32_t ub = u_addr + (k & 1) * C::U_BYTES + lane * 4;
 #pragma unroll
             for (int r = 0; r < 32; ++r) {
+                if (r < rb || r >= re) continue;
                 // slab row address = base + 136 * code in one integer dot-product instruction
-                const uint32_t addr = byte_scaled_add<US * 4>(rv[r >> 2], r & 3, ub);
+                const uint32_t addr = byte_scaled_add<US * 4>(rv[(r >> 2) & 3], r & 3, ub);
                 uint32_t word;
                 asm volatile("ld.shared.u32 %0, [%1];" : "=r"(word) : "r"(addr));
                 acc[r][0] += word;
                 acc[r][1] += word >> 16;
             }
-            if (kk == KC - 2 && have_next_chunk) store_chunk(stage ^ 1);
-            __syncthreads();
+        };
+
+        for (int k = kbeg; k < kend; ++k) {
+            const int chunk = k / KC, kk = k % KC, stage = chunk & 1;
+            const bool have_next_chunk = (chunk + 1) * KC < kend;
+            if (kk == 0 && have_next_chunk) fetch_chunk(m0, n0, chunk + 1);
+            if (HANDOVER) {
+                // phase of either barrier that belongs to this step: its (kl / 2)-th since the item began
+                const int b = k & 1;
+                const uint32_t par = ((k - kbeg) >> 1) & 1;
+                mbar_wait(bar_full + 8 * b, par, 11 + b, abort_word, p.error_word);         // slab k is complete
+                use_rows(k, stage, kk, 0, 16);
+                mbar_wait(bar_empty + 8 * (b ^ 1), par, 13 + b, abort_word, p.error_word);  // slab k-1 is released
+                if (k + 1 < kend) {
+                    build((k + 1) & 1, ((k + 1) / KC) & 1, (k + 1) % KC);
+                    if (kk == KC - 2 && have_next_chunk) store_chunk(stage ^ 1);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_full + 8 * (b ^ 1));
+                }
+                use_rows(k, stage, kk, 16, 32);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_empty + 8 * b);
+            } else {
+                if (k + 1 < kend) build((k + 1) & 1, ((k + 1) / KC) & 1, (k + 1) % KC);
+                use_rows(k, stage, kk, 0, 16);
+                use_rows(k, stage, kk, 16, 32);
+                if (kk == KC - 2 && have_next_chunk) store_chunk(stage ^ 1);
+                __syncthreads();
+            }
         }
 
         const int n = n0 + 2 * lane;
+        LayerEpilogueScalars ev{};
+        if (p.epi.out) ev = load_epilogue_scalars(p.epi);
 #pragma unroll
         for (int r = 0; r < 32; ++r) {
             acc[r][0] -= acc[r][1] << 16;  // low-half sum = whole-word sum - 65536 * high-half sum
             const int m = m0 + wp * 32 + r;
             if (m < M) {
+                if (p.epi.out) {
+                    // the layer's de-quantisation applied to the sums in registers (one split per tile here)
+                    const int l = m % p.epi.L;
+                    const float zw_box = __fmul_rn(ev.zw, p.epi.box[m]), zz_taps = __fmul_rn(ev.zz, p.epi.taps[l]);
+                    float *orow = p.epi.out + (size_t)m * N;
+                    if (n < N) orow[n] = epilogue_value(p.epi, ev, acc[r][0], zw_box, zz_taps, l, n, N);
+                    if (n + 1 < N) orow[n + 1] = epilogue_value(p.epi, ev, acc[r][1], zw_box, zz_taps, l, n + 1, N);
+                    continue;
+                }
                 uint32_t *crow = p.c + (size_t)m * N;
                 if (p.ksplits > 1) {
                     if (n < N) atomicAdd(crow + n, acc[r][0]);
@@ -218,25 +284,13 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p) {
 
 }  // namespace sf
 
-template <int BITS>
-static int launch_fwd_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int M, int K, int N,
-                           const ConvGeom &conv, const uint8_t *at, int at_pitch, int num_sms, cudaStream_t stream) {
-    using C = sf::Cfg<BITS>;
-    auto kern = at ? sf::slab_fwd_kernel<BITS, true> : sf::slab_fwd_kernel<BITS, false>;
-    if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM)))
-        return LUTGEMM_E_CUDA;
-    sf::Args p{};
-    p.a = a; p.w = w; p.lut = lut; p.c = c; p.M = M; p.K = K; p.N = N;
-    p.conv = conv;
-    p.at = at;
-    p.at_pitch = at_pitch;
-    p.tiles_r = (M + C::RT - 1) / C::RT;
-    p.tiles_c = (N + C::CT - 1) / C::CT;
-    const long tiles = (long)p.tiles_r * p.tiles_c;
-    // pick the K split that best fills the last wave of the persistent grid
+// the K split that best fills the last wave of the persistent grid (1 = every tile sums its whole K range)
+int slab_fwd_ksplits(int M, int K, int N, int num_sms) {
+    using C = sf::Cfg<8>;  // tile geometry does not depend on the bit-width
+    const long tiles = (long)((M + C::RT - 1) / C::RT) * ((N + C::CT - 1) / C::CT);
+    const int kchunks = (K + C::KC - 1) / C::KC;
     int ksplits = 1;
     double best = -1.0;
-    const int kchunks = (K + C::KC - 1) / C::KC;
     for (int s = 1; s <= 16 && s <= kchunks; ++s) {
         const int per = ((kchunks + s - 1) / s) * C::KC;
         if ((K + per - 1) / per != s) continue;  // some split would get no work
@@ -245,6 +299,35 @@ static int launch_fwd_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, cons
         const double eff = (double)items / (double)(waves * num_sms) * (double)per / (double)(per + 6);
         if (eff > best + 1e-9) { best = eff; ksplits = s; }
     }
+    return ksplits;
+}
+
+static bool g_fwd_handover = false;  // per-buffer mbarrier hand-over; measured slower than one CTA barrier per k here
+void slab_fwd_set_handover(bool on) { g_fwd_handover = on; }
+
+template <int BITS>
+static int launch_fwd_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int M, int K, int N,
+                           const ConvGeom &conv, const uint8_t *at, int at_pitch, const LayerEpilogue *epi, int num_sms,
+                           cudaStream_t stream) {
+    using C = sf::Cfg<BITS>;
+    auto kern = at ? (g_fwd_handover ? sf::slab_fwd_kernel<BITS, true, true> : sf::slab_fwd_kernel<BITS, true, false>)
+                   : (g_fwd_handover ? sf::slab_fwd_kernel<BITS, false, true> : sf::slab_fwd_kernel<BITS, false, false>);
+    if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM)))
+        return LUTGEMM_E_CUDA;
+    sf::Args p{};
+    p.a = a; p.w = w; p.lut = lut; p.c = c; p.M = M; p.K = K; p.N = N;
+    p.conv = conv;
+    p.at = at;
+    p.at_pitch = at_pitch;
+    p.error_word = device_error_word();
+    if (!p.error_word) return LUTGEMM_E_CUDA;
+    if (epi) p.epi = *epi;
+    p.tiles_r = (M + C::RT - 1) / C::RT;
+    p.tiles_c = (N + C::CT - 1) / C::CT;
+    const long tiles = (long)p.tiles_r * p.tiles_c;
+    const int kchunks = (K + C::KC - 1) / C::KC;
+    // (with a fused epilogue every tile must hold complete sums: the caller only asks for it when no K split pays)
+    const int ksplits = epi ? 1 : slab_fwd_ksplits(M, K, N, num_sms);
     p.ksplits = ksplits;
     p.k_per_split = ((kchunks + ksplits - 1) / ksplits) * C::KC;
     const long items = tiles * ksplits;
@@ -259,12 +342,13 @@ static int launch_fwd_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, cons
 }
 
 int forward_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int bits, int M, int K, int N,
-                 const ConvGeom &conv, const uint8_t *at, int at_pitch, int num_sms, cudaStream_t stream) {
+                 const ConvGeom &conv, const uint8_t *at, int at_pitch, const LayerEpilogue *epi, int num_sms,
+                 cudaStream_t stream) {
     switch (bits) {
-        case 4: return launch_fwd_slab<4>(a, w, c, lut, M, K, N, conv, at, at_pitch, num_sms, stream);
-        case 6: return launch_fwd_slab<6>(a, w, c, lut, M, K, N, conv, at, at_pitch, num_sms, stream);
-        case 7: return launch_fwd_slab<7>(a, w, c, lut, M, K, N, conv, at, at_pitch, num_sms, stream);
-        case 8: return launch_fwd_slab<8>(a, w, c, lut, M, K, N, conv, at, at_pitch, num_sms, stream);
+        case 4: return launch_fwd_slab<4>(a, w, c, lut, M, K, N, conv, at, at_pitch, epi, num_sms, stream);
+        case 6: return launch_fwd_slab<6>(a, w, c, lut, M, K, N, conv, at, at_pitch, epi, num_sms, stream);
+        case 7: return launch_fwd_slab<7>(a, w, c, lut, M, K, N, conv, at, at_pitch, epi, num_sms, stream);
+        case 8: return launch_fwd_slab<8>(a, w, c, lut, M, K, N, conv, at, at_pitch, epi, num_sms, stream);
     }
     return LUTGEMM_E_BITS;
 }

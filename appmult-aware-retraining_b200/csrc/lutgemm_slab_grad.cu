@@ -63,7 +63,7 @@ struct Args {
     int direct;
     int vec_a, vec_w, vec_g;
     ConvGeom conv;
-    int ga_bkl;
+    int ga_scatter;  // grad_a of a convolution: results go straight to the image gradient
     const uint8_t *at;  // grad_w only, optional: transposed row codes at[k][m], rows at_pitch bytes apart
     int at_pitch;       // a multiple of 16; columns m >= M hold 0
 };
@@ -105,10 +105,10 @@ __global__ void __launch_bounds__(32 * WARPS, 1) slab_grad_kernel(const Args p) 
         }
     }
 
-    auto ga_index = [&](int m, int k) -> size_t {
-        if (!p.ga_bkl) return (size_t)m * K + k;
-        const int L = p.conv.Ho * p.conv.Wo, b = m / L;
-        return ((size_t)b * K + k) * L + (m - b * L);
+    // grad_a of a convolution (non-overlapping windows) goes straight to its place in the image gradient
+    auto ga_index = [&](int m, int k) -> long {
+        if (!p.ga_scatter) return (long)m * K + k;
+        return conv_scatter_index(p.conv, m, k);
     };
 
     // ---- operand chunk staging: rc_s[stage][kk][r] (512 row codes per k), cc_s[stage][kk][c] (64) ------
@@ -229,8 +229,12 @@ __global__ void __launch_bounds__(32 * WARPS, 1) slab_grad_kernel(const Args p) 
 #pragma unroll
         for (int d = CPW; d < 32; d *= 2) v += __shfl_xor_sync(0xffffffffu, v, d);
         if (lane < CPW && c0 + col < CDIM) {
-            if (p.direct && MODE == kGa) obase[ga_index(c0 + col, k)] = v * kGradFactor;
-            else obase[(size_t)k * CDIM + c0 + col] = p.direct ? v * kGradFactor : v;
+            if (p.direct && MODE == kGa) {
+                const long o = ga_index(c0 + col, k);
+                if (o >= 0) obase[o] = v * kGradFactor;
+            } else {
+                obase[(size_t)k * CDIM + c0 + col] = p.direct ? v * kGradFactor : v;
+            }
         }
     };
 
@@ -353,10 +357,16 @@ __global__ void __launch_bounds__(32 * WARPS, 1) slab_grad_kernel(const Args p) 
 int slab_f32_row_blocks(int rdim) { return (rdim + kSlabF32Rows - 1) / kSlabF32Rows; }
 
 // out[k][c] (TRANSPOSE=false) or out[c][k] (TRANSPOSE=true) = scale * sum_b part[b][k][c], b ascending.
-// With bkl_L > 0 (and TRANSPOSE=false) column c = b*L + l goes to out[(b*K + k)*L + l] instead.
-template <bool TRANSPOSE>
+// PLACE = 1: column c is an unfolded row m of a convolution with non-overlapping windows and (m,k) goes to its
+// position in the image gradient (conv_scatter_index); PLACE = 2: column c is pixel c of a stride class and k a
+// channel (pixel_class_offset).  Both with TRANSPOSE=false.
+struct ReducePlace {
+    ConvGeom conv;
+    PixelClass px;
+};
+template <bool TRANSPOSE, int PLACE>
 __global__ void slab_reduce_blocks_kernel(const float *__restrict__ part, float *__restrict__ out, int K, int C,
-                                          int nblocks, float scale, int bkl_L) {
+                                          int nblocks, float scale, const ReducePlace pl) {
     __shared__ float tile[32][33];
     const int tiles_c = (C + 31) / 32, tiles_k = (K + 31) / 32;
     const size_t KC_ = (size_t)K * C;
@@ -371,8 +381,14 @@ __global__ void slab_reduce_blocks_kernel(const float *__restrict__ part, float 
                 for (int b = 0; b < nblocks; ++b) s += part[(size_t)b * KC_ + (size_t)k * C + c];
             if (TRANSPOSE) tile[ty + 8 * j][tx] = s * scale;
             else if (k < K && c < C) {
-                if (bkl_L > 0) out[((size_t)(c / bkl_L) * K + k) * bkl_L + c % bkl_L] = s * scale;
-                else out[(size_t)k * C + c] = s * scale;
+                if (PLACE == 1) {
+                    const long o = conv_scatter_index(pl.conv, c, k);
+                    if (o >= 0) out[o] = s * scale;
+                } else if (PLACE == 2) {
+                    out[pixel_class_offset(pl.px, c) + (size_t)k * pl.px.H * pl.px.W] = s * scale;
+                } else {
+                    out[(size_t)k * C + c] = s * scale;
+                }
             }
         }
         if (TRANSPOSE) {
@@ -387,14 +403,22 @@ __global__ void slab_reduce_blocks_kernel(const float *__restrict__ part, float 
     }
 }
 
-int slab_reduce_blocks(const float *part, float *out, int K, int C, int nblocks, bool transpose, int bkl_L,
-                       int num_sms, cudaStream_t stream) {
+int slab_reduce_blocks(const float *part, float *out, int K, int C, int nblocks, bool transpose, const ConvGeom *scatter,
+                       const PixelClass *px, float scale, int num_sms, cudaStream_t stream) {
     const long tiles = (long)((K + 31) / 32) * ((C + 31) / 32);
     const int rgrid = (int)(tiles < 8L * num_sms ? tiles : 8L * num_sms);
-    if (transpose && bkl_L == 0)
-        slab_reduce_blocks_kernel<true><<<rgrid, 256, 0, stream>>>(part, out, K, C, nblocks, kGradFactor, 0);
-    else
-        slab_reduce_blocks_kernel<false><<<rgrid, 256, 0, stream>>>(part, out, K, C, nblocks, kGradFactor, bkl_L);
+    ReducePlace pl{};
+    if (scatter) {
+        pl.conv = *scatter;
+        slab_reduce_blocks_kernel<false, 1><<<rgrid, 256, 0, stream>>>(part, out, K, C, nblocks, scale, pl);
+    } else if (px) {
+        pl.px = *px;
+        slab_reduce_blocks_kernel<false, 2><<<rgrid, 256, 0, stream>>>(part, out, K, C, nblocks, scale, pl);
+    } else if (transpose) {
+        slab_reduce_blocks_kernel<true, 0><<<rgrid, 256, 0, stream>>>(part, out, K, C, nblocks, scale, pl);
+    } else {
+        slab_reduce_blocks_kernel<false, 0><<<rgrid, 256, 0, stream>>>(part, out, K, C, nblocks, scale, pl);
+    }
     return launch_status();
 }
 
@@ -412,7 +436,7 @@ static int launch_slab_grad_w(const float *gc, const uint8_t *a, const uint8_t *
     p.conv = conv;
     p.at = MODE == sg::kGw ? at : nullptr;
     p.at_pitch = at_pitch;
-    p.ga_bkl = (MODE == sg::kGa && conv.enabled) ? 1 : 0;
+    p.ga_scatter = (MODE == sg::kGa && conv.enabled) ? 1 : 0;
     p.tiles_r = (RDIM + C::RT - 1) / C::RT;
     p.tiles_c = (CDIM + C::CT - 1) / C::CT;
     p.direct = p.tiles_r == 1;
@@ -440,8 +464,8 @@ static int launch_slab_grad_w(const float *gc, const uint8_t *a, const uint8_t *
     kern<<<grid, C::THREADS, C::SMEM, stream>>>(p);
     if (launch_status() != LUTGEMM_OK) return LUTGEMM_E_CUDA;
     if (!p.direct)
-        return slab_reduce_blocks(scratch, out, K, CDIM, p.tiles_r, MODE == sg::kGa, p.ga_bkl ? conv.Ho * conv.Wo : 0,
-                                  num_sms, stream);
+        return slab_reduce_blocks(scratch, out, K, CDIM, p.tiles_r, MODE == sg::kGa, p.ga_scatter ? &conv : nullptr, nullptr,
+                                  kGradFactor, num_sms, stream);
     return LUTGEMM_OK;
 }
 

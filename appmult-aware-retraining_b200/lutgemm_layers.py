@@ -16,7 +16,8 @@ weight codes, a tap count) instead of three full convolutions - identical in exa
 layers go through the approximate multiplier too (`AppLinear`), which the reference's `QuantLinear`
 (:78-113) does not do; the convolution can use the fused implicit-im2col kernels instead of
 `F.unfold` (conv_impl="fused"), and the whole layer - quantisation, convolution, cross terms, scaling - can
-run as three kernels in the forward pass (conv_impl="layer").  Spatial padding is code 0 and therefore contributes LUT[0][w], as in the reference
+run as two kernels in the forward pass - quantisation prologue, LUT convolution with the de-quantisation
+applied where it stores (conv_impl="layer").  Spatial padding is code 0 and therefore contributes LUT[0][w], as in the reference
 (self_ops/ops_py/approx_ops.py:556)."""
 from __future__ import annotations
 
@@ -98,15 +99,14 @@ class _AppConvLayer(torch.autograd.Function):
         codes, chansum = approx_ops.quantize_activations(x, s_a, z_a, a_qmax)
         qw = torch.clamp(torch.round(weight / s_w - z_w), 0.0, w_qmax)
         wmat = qw.reshape(Cout, -1).t().to(torch.uint8).contiguous()
-        y = torch.empty((M, Cout), dtype=torch.uint32, device=x.device)
-        codes_t = approx_ops.approx_conv2d_forward(codes, wmat, y, _ops_state.lut_appmult, kh, kw, stride, padding,
-                                                   dilation)
         geom = (H, W, kh, kw, stride, padding, dilation)
         valid = _valid_taps(geom, x.device)                                   # [kh*kw, L]
         box = _window_sum(chansum, geom).reshape(M)
         sumw_t = (valid.t() @ qw.sum(dim=1).reshape(Cout, kh * kw).t()).contiguous()  # [L, Cout]
         taps = valid.sum(dim=0) * float(Cin)
-        out = approx_ops.conv2d_epilogue(y, box, sumw_t, taps, s_a, s_w, z_a, z_w, bias, L)
+        # one kernel: LUT convolution with the de-quantisation applied to the sums in registers
+        out, codes_t = approx_ops.approx_conv2d_forward_layer(codes, wmat, _ops_state.lut_appmult, kh, kw, stride, padding,
+                                                              dilation, box, sumw_t, taps, s_a, s_w, z_a, z_w, bias)
         ctx.save_for_backward(x, codes, wmat, weight, quant)
         ctx.codes_t = codes_t  # transposed unfolded codes of the forward kernel: the grad_w kernel reuses them
         ctx.cfg = (a_qmax, w_qmax, stride, padding, dilation, Ho, Wo, bias is not None)
@@ -165,12 +165,11 @@ class _AppLinearLayer(torch.autograd.Function):
         codes = codes.view(M, K)
         qw = torch.clamp(torch.round(weight / s_w - z_w), 0.0, w_qmax)
         wmat = qw.t().to(torch.uint8).contiguous()
-        y = torch.empty((M, N), dtype=torch.uint32, device=x2.device)
-        codes_t = approx_ops.approx_gemm_forward(codes, wmat, y, _ops_state.lut_appmult)
         box = codes.sum(dim=1, dtype=torch.float32)
         sumw_t = qw.sum(dim=1).view(1, N).contiguous()
         taps = torch.full((1,), float(K), device=x2.device)
-        out = approx_ops.conv2d_epilogue(y, box, sumw_t, taps, s_a, s_w, z_a, z_w, bias, 1)
+        out, codes_t = approx_ops.approx_gemm_forward_layer(codes, wmat, _ops_state.lut_appmult, box, sumw_t, taps, s_a, s_w,
+                                                            z_a, z_w, bias)
         ctx.save_for_backward(x2, codes, wmat, weight, quant)
         ctx.codes_t = codes_t  # transposed codes of the forward kernel: the grad_w kernel reuses them
         ctx.cfg = (a_qmax, w_qmax, bias is not None)

@@ -20,7 +20,7 @@ import torch.distributed as dist
 import torch.nn.functional as F
 
 import self_ops
-from lutgemm_dp import allreduce_grads_bucketed
+from lutgemm_dp import OverlappedGradReducer
 from lutgemm_layers import prepare
 from lutgemm_luts import synthetic_multiplier, window_difference_gradients
 from lutgemm_models import MODELS
@@ -45,11 +45,13 @@ def build(device, bits: int, conv_impl: str = "layer", use_ste: bool = False, lr
     return model, opt
 
 
-def train_step(model, opt, params, images, labels):
-    opt.zero_grad(set_to_none=True)
+def train_step(model, opt, reducer, images, labels):
+    """One step: forward, cross-entropy, backward with the bucketed gradient all-reduce launched from hooks
+    while backward runs (`reducer`: an OverlappedGradReducer over the model's parameters), optimizer step."""
+    reducer.zero_grad()
     loss = F.cross_entropy(model(images), labels)
     loss.backward()
-    allreduce_grads_bucketed(params)
+    reducer.finish()
     opt.step()
     return loss
 
@@ -88,13 +90,13 @@ def main():
     install_tables(device, args.bits, args.lut_file)
     model, opt = build(device, args.bits, args.conv_impl, args.ste, args.lr, args.model)
     _, image_shape, classes = MODELS[args.model]
-    params = [p for p in model.parameters() if p.requires_grad]
+    reducer = OverlappedGradReducer(model.parameters())
     g = torch.Generator().manual_seed(100 + rank)
     t0 = time.time()
     for step in range(args.steps):
         images = torch.randn(args.batch, *image_shape, generator=g).pin_memory().to(device, non_blocking=True)
         labels = torch.randint(0, classes, (args.batch,), generator=g).pin_memory().to(device, non_blocking=True)
-        loss = train_step(model, opt, params, images, labels)
+        loss = train_step(model, opt, reducer, images, labels)
         if rank == 0 and (step % 10 == 0 or step == args.steps - 1):
             print(f"step {step:4d}  loss {loss.item():.4f}  {world * args.batch * (step + 1) / (time.time() - t0):.0f} img/s",
                   flush=True)

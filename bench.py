@@ -539,7 +539,8 @@ def run_model(args, rank, world, local_rank):
     ctor, image_shape, classes = MODELS[args.workload]
     macs_img = lut_macs_per_image(ctor(classes).to(dev), image_shape)
     model, opt = build(dev, bits, conv_impl=args.conv_impl, use_ste=args.ste, model_name=args.workload)
-    params = [p for p in model.parameters() if p.requires_grad]
+    from lutgemm_dp import OverlappedGradReducer
+    reducer = OverlappedGradReducer(model.parameters())
     g = torch.Generator().manual_seed(100 + rank)
     nsets = 4
     imgs_h = [torch.randn(batch, *image_shape, generator=g).pin_memory() for _ in range(nsets)]
@@ -548,7 +549,7 @@ def run_model(args, rank, world, local_rank):
     lbls_d = [t.to(dev) for t in lbls_h]
 
     def step(x, y):
-        return train_step(model, opt, params, x, y)
+        return train_step(model, opt, reducer, x, y)
 
     def barrier():
         if world > 1:
@@ -588,6 +589,7 @@ def run_model(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms, e2e_ms = float(t[0]), float(t[1])
     err = approx_ops.device_error()
+    reducer.close()
     if rank != 0:
         return None
     peaks, peaks_kind = measured_peaks()
@@ -604,7 +606,8 @@ def run_model(args, rank, world, local_rank):
         "config": {"workload": f"{WORKLOAD_NAMES[args.workload]} AppMult training step, {bits}-bit, batch {batch}/GPU, SGD",
                    "bits": bits, "batch_per_gpu": batch, "conv_impl": args.conv_impl, "ste_backward": bool(args.ste),
                    "lut_macs_per_step_per_gpu": macs_step,
-                   "parallelism": f"dp{world} (batch sharded, bucketed NCCL all-reduce of gradients)" if world > 1 else "single GPU",
+                   "parallelism": (f"dp{world} (batch sharded, bucketed NCCL all-reduce of gradients launched from hooks during backward)"
+                                   if world > 1 else "single GPU"),
                    "l2": f"{nsets} rotating batches; activations of a step exceed L2"},
         "roofline": {"bound": "smem_lsu", "kernel": "whole step (LUT kernels + fp32 glue)",
                      "achieved": macs_step * args.steps / (total_ms * 1e-3) / 1e9, "peak": peak_lookups / 1e9,

@@ -55,6 +55,14 @@ unsigned long long lutgemm_kernel_launches(void);
 #define LUTGEMM_TILE_TALL 2
 int lutgemm_set_kernel_choice(int forward, int backward, int grad_tile);
 
+/*
+ * How the 16 warps of a slab-kernel CTA pass slab buffers to each other, process-wide: 1 (default) = through
+ * per-buffer shared-memory barriers with one arrival per warp, so warps may drift by half a read phase;
+ * 0 = one CTA-wide barrier per k.  Same results either way; exists for A/B timing and tests.
+ * No counterpart in the reference.
+ */
+int lutgemm_set_handover(int on);
+
 /* Human-readable text for a status code; for LUTGEMM_E_CUDA the CUDA error behind the calling thread's
  * last such status is appended.  The returned pointer is valid until the thread's next call. */
 const char *lutgemm_status_string(int status);
@@ -121,7 +129,23 @@ int lutgemm_backward_ws(const float *gc, const uint8_t *a, const uint8_t *w, flo
                         const uint8_t *codes_t, void *scratch, size_t scratch_bytes, void *stream);
 
 /*
- * Convolution forward with the im2col fused into the operand loader (no unfolded tensor in HBM):
+ * Backward with the gradient tables in fp32 (bit-widths up to 7): the same sums as lutgemm_backward with
+ * float(lut) replaced by the fp32 entry and without the 1/16 factor,
+ *   ga[m,k] = sum_n gc[m,n] * lut_ga[a[m,k]*(2^bits+2) + w[k,n]],   gw[k,n] = sum_m lut_gw[...] * gc[m,n].
+ * The tables use the padded flat layout of the wire format with float entries.  For callers whose gradient
+ * tables are not multiples of 1/16 (the reference rounds them to that grid when it writes its LUT files,
+ * scripts/gen_bp_lut.py:171-183, and its kernels only take the int16 form, approx_gemm_backward.cu:506-529).
+ * At 8 bits an fp32 table (256 KB) does not fit next to the slabs in shared memory: LUTGEMM_E_BITS.
+ * scratch: lutgemm_backward_f32lut_scratch_bytes() bytes, 16-byte aligned.  No counterpart in the reference.
+ */
+size_t lutgemm_backward_f32lut_scratch_bytes(int bits, int M, int K, int N);
+int lutgemm_backward_f32lut(const float *gc, const uint8_t *a, const uint8_t *w, float *ga, float *gw,
+                            const float *lut_ga, const float *lut_gw, int bits, int M, int K, int N, void *scratch,
+                            size_t scratch_bytes, void *stream);
+
+/*
+ * Convolution forward with the im2col fused into the operand loader (this entry point writes no unfolded
+ * tensor; lutgemm_conv2d_forward_ws below trades one uint8 copy of the unfolded codes for faster loads):
  *   y[(b*Ho+oh)*Wo+ow, n] = sum_{c,i,j} lut[ x[b,c,oh*stride-pad+i*dil,ow*stride-pad+j*dil] * (2^bits+2) + wmat[(c*kh+i)*kw+j, n] ]
  * with code 0 outside the image (spatial padding looks up lut[0][w], as in the reference).
  *   x    [B,C,H,W] uint8 codes (NCHW)       wmat [C*kh*kw, Cout] uint8 (the weight viewed [Cout,-1], transposed)
@@ -133,17 +157,22 @@ int lutgemm_conv2d_forward(const uint8_t *x, const uint8_t *wmat, uint32_t *y, c
                            int B, int C, int H, int W, int Cout, int kh, int kw, int stride, int pad, int dil,
                            void *stream);
 
-/* Scratch bytes lutgemm_conv2d_backward needs: the unfolded activation gradient [B][C*kh*kw][Ho*Wo] in
- * fp32 plus what the gradient kernels need.  No counterpart in the reference. */
+/* Scratch bytes lutgemm_conv2d_backward needs: per-row-block partial sums of the gradient kernels and, for the
+ * weight gradient, a transposed uint8 copy of the unfolded activation CODES (M*K bytes) when the caller passes
+ * none.  No fp32 unfolded gradient is ever materialised.  No counterpart in the reference. */
 size_t lutgemm_conv2d_backward_scratch_bytes(int bits, int B, int C, int H, int W, int Cout, int kh, int kw,
                                              int stride, int pad, int dil);
 
 /*
  * Convolution backward through the gradient tables, activations gathered on the fly as in the forward:
- *   gw[(c*kh+i)*kw+j, n] = 1/16 * sum_m lut_gw[a[m,k]][wmat[k,n]] * gy[m,n]          ([C*kh*kw, Cout] fp32)
- *   gx[b,c,h,w]          = col2im( 1/16 * sum_n gy[m,n] * lut_ga[a[m,k]][wmat[k,n]] )   ([B,C,H,W] fp32)
- *   gy [B*Ho*Wo, Cout] fp32 (NHWC).  gx or gw may be NULL.  The unfolded activation gradient lives in
- *   `scratch` ([B][K][Ho*Wo]) and is folded by a deterministic gather kernel.
+ *   gw[(c*kh+i)*kw+j, n] = 1/16 * sum_m lut_gw[a[m,k]][wmat[k,n]] * gy[m,n]                 ([C*kh*kw, Cout] fp32)
+ *   gx[b,c,h,w] = 1/16 * sum over the taps (i,j) that reach (h,w) and over n of
+ *                 gy[m(b,h,w,i,j), n] * lut_ga[x[b,c,h,w]][wmat[(c*kh+i)*kw+j, n]]          ([B,C,H,W] fp32)
+ *   gy [B*Ho*Wo, Cout] fp32 (NHWC).  gx or gw may be NULL.
+ * gx is computed per input pixel (every tap that touches a pixel sees the same activation code, so the sum over
+ * taps joins the sum over n); the unfolded activation gradient [B*Ho*Wo, C*kh*kw] the reference forms and folds
+ * back (autograd of F.unfold) never exists.  Overlapping windows with more than 128 taps are refused
+ * (LUTGEMM_E_TOOLARGE).  Sums are deterministic.
  * Replaces the autograd chain of approx_conv2d_op (unfold backward + approx_gemm_backward),
  * self_ops/ops_py/approx_ops.py:181-205,556-571.
  */
@@ -209,6 +238,32 @@ int lutgemm_quantize_activations_backward(const float *x, long stride_b, long st
 int lutgemm_conv2d_epilogue(const uint32_t *y, const float *box, const float *sumw_t, const float *taps,
                             const float *s_a, const float *s_w, const float *z_a, const float *z_w, const float *bias,
                             float *out, long M, int L, int Cout, void *stream);
+
+/*
+ * Forward of a whole approximate layer in one kernel: lutgemm_conv2d_forward_ws (or lutgemm_forward_ws for a
+ * linear layer, L = 1) with lutgemm_conv2d_epilogue applied to the sums while they are still in registers, so the
+ * uint32 accumulators [M, Cout] are neither written nor read back:
+ *   out[m,co] = *s_a * *s_w * (sum[m,co] + *z_w * box[m] + *z_a * sumw_t[l,co] + *z_a * *z_w * taps[l]) (+ bias[co])
+ * with m = b*L + l; arguments as for the two functions it combines.  scratch: lutgemm_*_forward_layer_scratch_bytes()
+ * bytes, 16-byte aligned: first the transposed-codes workspace of lutgemm_conv2d_forward_scratch_bytes /
+ * lutgemm_forward_scratch_bytes (valid on return, reusable by the backward of the same layer), then - only for
+ * shapes with so few output tiles that the kernel cuts K across CTAs, whose partial sums have to meet in memory -
+ * room for the uint32 sums, which the one-pass epilogue kernel then finishes.  scratch may be NULL when the
+ * function returns 0 bytes.
+ * Replaces self_ops.approx_conv2d_op's forward plus micronet+/app_layers.py:175-184.
+ */
+size_t lutgemm_conv2d_forward_layer_scratch_bytes(int bits, int B, int C, int H, int W, int Cout, int kh, int kw,
+                                                  int stride, int pad, int dil);
+size_t lutgemm_forward_layer_scratch_bytes(int bits, int M, int K, int N);
+int lutgemm_conv2d_forward_layer(const uint8_t *x, const uint8_t *wmat, const uint16_t *lut, int bits, int B, int C, int H,
+                                 int W, int Cout, int kh, int kw, int stride, int pad, int dil, const float *box,
+                                 const float *sumw_t, const float *taps, const float *s_a, const float *s_w,
+                                 const float *z_a, const float *z_w, const float *bias, float *out, void *scratch,
+                                 size_t scratch_bytes, void *stream);
+int lutgemm_forward_layer(const uint8_t *a, const uint8_t *w, const uint16_t *lut, int bits, int M, int K, int N,
+                          const float *box, const float *sumw_t, const float *taps, const float *s_a, const float *s_w,
+                          const float *z_a, const float *z_w, const float *bias, float *out, void *scratch,
+                          size_t scratch_bytes, void *stream);
 
 /*
  * Weight gradient only, with no device memory taken from anyone: same result as lutgemm_backward with

@@ -83,3 +83,69 @@ def test_shard_rows_partitions():
             assert max(sizes) - min(sizes) <= 1
     with pytest.raises(ValueError):
         shard_rows(4, 2, 2)
+
+
+def _hook_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT); sys.path.insert(0, os.path.join(ROOT, "appmult-aware-retraining_b200"))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from lutgemm_dp import OverlappedGradReducer
+    torch.manual_seed(0)  # same initial weights on every rank
+    model = torch.nn.Sequential(torch.nn.Linear(6, 8), torch.nn.Tanh(), torch.nn.Linear(8, 5), torch.nn.Tanh(),
+                                torch.nn.Linear(5, 3))
+    reducer = OverlappedGradReducer(model.parameters(), bucket_bytes=200)  # several buckets
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    steps = []
+    for step in range(3):
+        x = torch.randn(4, 6, generator=torch.Generator().manual_seed(10 * step + rank))
+        if step == 1:
+            opt.zero_grad(set_to_none=True)  # a caller that detaches .grad from the buffer is folded back in
+        else:
+            reducer.zero_grad()
+        model(x).square().sum().backward()
+        local = [p.grad.clone() for p in model.parameters()]  # not yet final: collectives may be in flight
+        ncoll = reducer.finish()
+        steps.append((ncoll, [p.grad.clone().numpy() for p in model.parameters()]))
+        assert all(p.grad.data_ptr() >= reducer.flat.data_ptr() for p in model.parameters())
+        opt.step()
+    # reference: the same three steps with gradients averaged by plain per-tensor all-reduce
+    torch.manual_seed(0)
+    model2 = torch.nn.Sequential(torch.nn.Linear(6, 8), torch.nn.Tanh(), torch.nn.Linear(8, 5), torch.nn.Tanh(),
+                                 torch.nn.Linear(5, 3))
+    opt2 = torch.optim.SGD(model2.parameters(), lr=0.1)
+    want = []
+    for step in range(3):
+        x = torch.randn(4, 6, generator=torch.Generator().manual_seed(10 * step + rank))
+        opt2.zero_grad(set_to_none=True)
+        model2(x).square().sum().backward()
+        for p in model2.parameters():
+            dist.all_reduce(p.grad)
+            p.grad.div_(world)
+        want.append([p.grad.clone().numpy() for p in model2.parameters()])
+        opt2.step()
+    ret[f"steps{rank}"] = steps
+    ret[f"want{rank}"] = want
+    ret[f"buckets{rank}"] = len(reducer.buckets)
+    reducer.close()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_overlapped_grad_reducer_matches_per_tensor_allreduce():
+    """Hook-driven bucketed all-reduce into the persistent flat gradient buffer (world size 2, gloo) against a
+    plain per-tensor all-reduce after backward, over three optimizer steps."""
+    world = 2
+    port = 31500 + os.getpid() % 2000
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_hook_worker, args=(world, port, ret), nprocs=world, join=True)
+        ret = dict(ret)
+    assert ret["buckets0"] >= 2
+    for r in range(world):
+        for (ncoll, got), want in zip(ret[f"steps{r}"], ret[f"want{r}"]):
+            assert ncoll == ret["buckets0"]
+            for g_, w_ in zip(got, want):
+                assert np.allclose(g_, w_, rtol=1e-6, atol=1e-7)
+    for (_, g0), (_, g1) in zip(ret["steps0"], ret["steps1"]):  # both ranks hold the same averaged gradients
+        for a_, b_ in zip(g0, g1):
+            assert np.array_equal(a_, b_)

@@ -67,6 +67,46 @@ def test_config0_signed_linear_layer(dev):
     assert (np.abs(g_w.cpu().numpy() - ref_w) <= TOL * abs_w + 1e-30).all()
 
 
+@pytest.mark.parametrize("bits,shape", [(7, (256, 512, 256)), (6, (1030, 70, 45)), (4, (33, 129, 2100)), (7, (2500, 64, 96))])
+def test_fp32_gradient_tables(dev, bits, shape):
+    """lutgemm_backward_f32lut with the benchmark's un-rounded window-difference gradient tables (fp32 entries
+    that are not multiples of 1/16) against their definition evaluated in float64:
+    ga[m,k] = sum_n gc[m,n] * Ga[a[m,k]][w[k,n]], gw[k,n] = sum_m Gw[a[m,k]][w[k,n]] * gc[m,n]; tolerance 1e-5
+    of the sum of the absolute terms of each element."""
+    import approx_ops
+    M, K, N = shape
+    q = 1 << bits
+    _, ga_t, gb_t = O.synthetic_tables(bits, seed=bits, half_window=3 if bits == 4 else q // 16)
+    ga_t, gb_t = ga_t.astype(np.float32), gb_t.astype(np.float32)
+    assert np.abs(ga_t * 16 - np.round(ga_t * 16)).max() > 1e-3  # really off the 1/16 grid
+    n_el = approx_ops.library().lutgemm_lut_elem_num(bits)
+
+    def wire(dense):
+        flat = np.zeros(n_el, np.float32)
+        flat[: (q + 1) * (q + 2)].reshape(q + 1, q + 2)[:q, :q] = dense
+        return torch.from_numpy(flat).to(dev)
+
+    rng = np.random.default_rng(5 * bits + M)
+    a, w = rng.integers(0, q, (M, K)).astype(np.uint8), rng.integers(0, q, (K, N)).astype(np.uint8)
+    gc = rng.standard_normal((M, N)).astype(np.float32)
+    ga = torch.full((M, K), float("nan"), device=dev)
+    gw = torch.full((K, N), float("nan"), device=dev)
+    approx_ops.approx_gemm_backward_f32lut(torch.from_numpy(gc).to(dev), torch.from_numpy(a).to(dev),
+                                           torch.from_numpy(w).to(dev), ga, gw, wire(ga_t), wire(gb_t))
+    gc64, Ga, Gw = gc.astype(np.float64), ga_t.astype(np.float64), gb_t.astype(np.float64)
+    ref_a, abs_a, ref_w, abs_w = np.zeros((M, K)), np.zeros((M, K)), np.zeros((K, N)), np.zeros((K, N))
+    for k in range(K):
+        ta = Ga[a[:, k, None], w[None, k, :]] * gc64
+        tw = Gw[a[:, k, None], w[None, k, :]] * gc64
+        ref_a[:, k], abs_a[:, k] = ta.sum(axis=1), np.abs(ta).sum(axis=1)
+        ref_w[k, :], abs_w[k, :] = tw.sum(axis=0), np.abs(tw).sum(axis=0)
+    assert (np.abs(ga.cpu().numpy() - ref_a) <= TOL * abs_a + 1e-30).all()
+    assert (np.abs(gw.cpu().numpy() - ref_w) <= TOL * abs_w + 1e-30).all()
+    # 8-bit fp32 tables do not fit in shared memory next to the slabs: refused, not approximated
+    lib = approx_ops.library()
+    assert lib.lutgemm_backward_f32lut(1, 1, 1, 1, 1, 1, 1, 8, 4, 4, 4, None, 0, None) == -2
+
+
 def _check_gemm(dev, oracle_c, bits, M, K, N, seed, tables):
     import approx_ops
     lf, la, lw = tables

@@ -224,7 +224,15 @@ def test_autograd_ops_and_conv_against_golden(dev, golden):
 CONV_CASES = [  # B, Cin, H, W, Cout, k, stride, pad, dil
     (2, 3, 8, 8, 5, 3, 1, 1, 1), (1, 4, 9, 7, 6, 3, 2, 1, 1), (2, 2, 6, 6, 3, 1, 1, 0, 1), (1, 3, 10, 10, 4, 3, 1, 2, 2),
     (3, 3, 32, 32, 64, 3, 1, 1, 1), (2, 16, 16, 16, 40, 3, 2, 1, 1), (4, 8, 12, 12, 32, 1, 2, 0, 1),
-    (2, 64, 16, 16, 64, 3, 1, 1, 1), (1, 24, 20, 20, 400, 3, 1, 1, 1), (2, 5, 7, 9, 33, 5, 1, 2, 1)]
+    (2, 64, 16, 16, 64, 3, 1, 1, 1), (1, 24, 20, 20, 400, 3, 1, 1, 1), (2, 5, 7, 9, 33, 5, 1, 2, 1),
+    # activation gradient without an unfolded intermediate: several row blocks per pixel tile (3x3, 128 and 320
+    # output channels), stride classes with 1 to 16 taps (3x3, 5x5 and 7x7 at stride 2, 4x4 at stride 3)
+    (2, 20, 10, 10, 128, 3, 1, 1, 1), (1, 8, 16, 16, 320, 3, 2, 1, 1), (2, 6, 11, 13, 24, 5, 2, 2, 1),
+    (1, 3, 21, 18, 16, 7, 2, 3, 1), (2, 4, 13, 11, 12, 4, 3, 1, 1),
+    # windows that do not overlap (grad_a written in place): 2x2 stride 2, 4x4 stride 4 (patches), 3x3 stride 3
+    # with padding, 2x2 stride 3 (positions nobody reads), 1x1 with a long reduction (slab kernels)
+    (2, 5, 8, 8, 9, 2, 2, 0, 1), (1, 3, 16, 16, 40, 4, 4, 0, 1), (2, 4, 10, 10, 7, 3, 3, 1, 1),
+    (1, 6, 11, 11, 10, 2, 3, 0, 1), (1, 8, 12, 12, 800, 1, 1, 0, 1)]
 
 
 @pytest.mark.parametrize("bits", [4, 6, 7, 8])

@@ -6,9 +6,11 @@ The entry point serves callers that may not allocate device memory when the weig
 host runtime with a fixed memory budget, a binding that cannot reach the framework's allocator, a path
 where cudaMalloc's implicit synchronisation is unacceptable): its partial sums go to a fixed 32 MiB array
 inside the library instead of a scratch buffer from the caller.  Checked here: two calls in a row give
-the same weight gradient as the regular entry point with a caller-allocated scratch buffer, to the
-tolerance the other gradient tests use (1e-5); PyTorch's allocator sees no allocation during the calls;
-problems whose partial sums exceed the array are refused."""
+the same weight gradient as the regular entry point with a caller-allocated scratch buffer and as the CPU
+oracle, to the tolerance the other gradient tests use (1e-5); the driver's count of free device memory does
+not move across the calls (cudaMemGetInfo sees every allocation, whoever makes it - PyTorch's own counters
+would only see PyTorch's); a call on a second stream gives the same result; problems whose partial sums
+exceed the array are refused."""
 import ctypes
 
 import numpy as np
@@ -30,9 +32,10 @@ def _problem(dev, bits, M, K, N, seed):
     return a, w, gc, torch.from_numpy(lw).to(dev)
 
 
-def test_no_alloc_weight_gradient_matches_regular_entry_point_twice_in_a_row():
+def test_no_alloc_weight_gradient_matches_regular_entry_point_twice_in_a_row(oracle_c):
     assert torch.cuda.is_available(), "gpu-marked test started without a CUDA device"
     import approx_ops
+    from oracle import oracle_np as O
     lib = approx_ops.library()
     vp, ci = ctypes.c_void_p, ctypes.c_int
     lib.lutgemm_backward_gw_noalloc.restype = ci
@@ -57,16 +60,36 @@ def test_no_alloc_weight_gradient_matches_regular_entry_point_twice_in_a_row():
                                   bits, M, K, N, scratch.data_ptr(), nbytes, stream)
         assert rc == 0
         got = torch.full((K, N), float("nan"), device=dev)
-        torch.cuda.synchronize()
-        before = torch.cuda.memory_allocated(dev)
+        got2 = torch.full((K, N), float("nan"), device=dev)
+        side = torch.cuda.Stream(dev)
+        # one call first: it looks up the array's address on this device and makes the driver load the kernels,
+        # which may take device memory once per process; the calls measured below must take none
         rc = lib.lutgemm_backward_gw_noalloc(gc.data_ptr(), a.data_ptr(), w.data_ptr(), got.data_ptr(), lw.data_ptr(),
                                              bits, M, K, N, stream)
         assert rc == 0, lib.lutgemm_status_string(rc)
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated(dev) == before
+        got.fill_(float("nan"))
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info(dev)[0]
+        torch_before = torch.cuda.memory_allocated(dev)
+        rc = lib.lutgemm_backward_gw_noalloc(gc.data_ptr(), a.data_ptr(), w.data_ptr(), got.data_ptr(), lw.data_ptr(),
+                                             bits, M, K, N, stream)
+        assert rc == 0, lib.lutgemm_status_string(rc)
+        torch.cuda.synchronize()  # the calls share the one array: the second starts after the first has finished
+        rc = lib.lutgemm_backward_gw_noalloc(gc.data_ptr(), a.data_ptr(), w.data_ptr(), got2.data_ptr(), lw.data_ptr(),
+                                             bits, M, K, N, side.cuda_stream)
+        assert rc == 0, lib.lutgemm_status_string(rc)
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info(dev)[0] == free_before, "device memory was taken during the calls"
+        assert torch.cuda.memory_allocated(dev) == torch_before
         ref_n, got_n = ref.cpu().numpy(), got.cpu().numpy()
         assert np.isfinite(got_n).all()
         assert np.abs(got_n - ref_n).max() <= TOL * max(np.abs(ref_n).max(), 1e-30)
+        assert torch.equal(got, got2), "the call on a second stream gave another result"
+        # and against the CPU oracle (weight gradient only; its float64 sums and the sums of absolute terms)
+        _, r_gw, _, r_gwa = oracle_c.backward_f64(gc.cpu().numpy(), a.cpu().numpy(), w.cpu().numpy(),
+                                                  np.zeros_like(lw.cpu().numpy()), lw.cpu().numpy(), bits)
+        assert (np.abs(got_n - r_gw) <= TOL * r_gwa + 1e-30).all()
     assert approx_ops.device_error() == 0
 
 
