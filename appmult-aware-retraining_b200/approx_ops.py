@@ -36,7 +36,7 @@ def _load():
             f"{_LIB_PATH} is missing: build it with `python {os.path.join(_HERE, 'build_ext.py')}` "
             "(there is no fallback path for the LUT-GEMM operators)")
     lib = ctypes.CDLL(_LIB_PATH)
-    vp, ci, cl, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_size_t
+    vp, ci, cl, sz, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_size_t, ctypes.c_float
     lib.lutgemm_version.restype = ci
     lib.lutgemm_status_string.restype = ctypes.c_char_p
     lib.lutgemm_status_string.argtypes = [ci]
@@ -77,6 +77,18 @@ def _load():
     lib.lutgemm_conv2d_epilogue.argtypes = [vp] * 10 + [cl, ci, ci, vp]
     lib.lutgemm_kernel_launches.restype = ctypes.c_ulonglong
     lib.lutgemm_kernel_launches.argtypes = []
+    lib.lutgemm_layer_update_ranges.restype = ci
+    lib.lutgemm_layer_update_ranges.argtypes = [vp] * 10 + [cf] * 5 + [vp, vp]
+    lib.lutgemm_layer_weight_prep.restype = ci
+    lib.lutgemm_layer_weight_prep.argtypes = [vp, cl, cl, cl, cl, ci, ci, ci, ci, vp, cf, vp, vp, vp]
+    lib.lutgemm_layer_cross_terms.restype = ci
+    lib.lutgemm_layer_cross_terms.argtypes = [vp] + [ci] * 9 + [vp, vp, vp]
+    lib.lutgemm_layer_window_sum.restype = ci
+    lib.lutgemm_layer_window_sum.argtypes = [vp] + [ci] * 8 + [vp, vp]
+    lib.lutgemm_layer_window_sum_adjoint.restype = ci
+    lib.lutgemm_layer_window_sum_adjoint.argtypes = [vp] + [ci] * 8 + [vp, vp]
+    lib.lutgemm_layer_weight_grad.restype = ci
+    lib.lutgemm_layer_weight_grad.argtypes = [vp, vp, vp, cl, cl, cl, cl, ci, ci, ci, ci, vp, cf, vp, vp]
     lib.lutgemm_conv2d_forward_layer_scratch_bytes.restype = sz
     lib.lutgemm_conv2d_forward_layer_scratch_bytes.argtypes = [ci] * 11
     lib.lutgemm_forward_layer_scratch_bytes.restype = sz
@@ -89,6 +101,8 @@ def _load():
     lib.lutgemm_backward_f32lut_scratch_bytes.argtypes = [ci, ci, ci, ci]
     lib.lutgemm_backward_f32lut.restype = ci
     lib.lutgemm_backward_f32lut.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp, sz, vp]
+    lib.lutgemm_set_tma.restype = ci
+    lib.lutgemm_set_tma.argtypes = [ci]
     lib.lutgemm_set_handover.restype = ci
     lib.lutgemm_set_handover.argtypes = [ci]
     lib.lutgemm_set_kernel_choice.restype = ci
@@ -494,3 +508,90 @@ def conv2d_epilogue(y: torch.Tensor, box: torch.Tensor, sumw_t: torch.Tensor, ta
                                              _stream_ptr(y.device))
     _check(rc, "conv2d_epilogue")
     return out
+
+
+# ---- small one-pass kernels of the layer wiring (lutgemm_layers.py) ---------------------------------------------------
+def layer_update_ranges(act_lo, act_hi, w_lo, w_hi, act_state, w_state, momentum: float, a_qmax: float, w_qmax: float,
+                        quant: torch.Tensor) -> None:
+    """Observers and quantisation parameters of one layer in one launch.  act_lo / act_hi / w_lo / w_hi: device
+    scalars (this batch's activation range, the weights' range); act_state / w_state: (min, max, seen) buffers,
+    updated in place - exponential moving average for activations, running range for weights; quant (4 floats) =
+    {s_a, z_a, s_w, z_w}."""
+    dev = quant.device
+    eps = float(torch.finfo(torch.float32).eps)
+    with torch.cuda.device(dev):
+        rc = _load().lutgemm_layer_update_ranges(
+            act_lo.data_ptr(), act_hi.data_ptr(), w_lo.data_ptr(), w_hi.data_ptr(), act_state[0].data_ptr(),
+            act_state[1].data_ptr(), act_state[2].data_ptr(), w_state[0].data_ptr(), w_state[1].data_ptr(),
+            w_state[2].data_ptr(), float(1 - momentum), float(momentum), float(a_qmax), float(w_qmax), eps,
+            quant.data_ptr(), _stream_ptr(dev))
+    _check(rc, "layer_update_ranges")
+
+
+def layer_weight_prep(weight: torch.Tensor, quant: torch.Tensor, qmax: float):
+    """(wmat u8 [Cin*kh*kw, Cout], wsum f32 [Cout, kh*kw]) of a 4-D fp32 weight in any dense layout: the weight
+    codes transposed for the LUT kernels and their sums over the input channels per tap."""
+    Cout, Cin, kh, kw = weight.shape
+    wmat = torch.empty((Cin * kh * kw, Cout), dtype=torch.uint8, device=weight.device)
+    wsum = torch.empty((Cout, kh * kw), dtype=torch.float32, device=weight.device)
+    s = weight.stride()
+    with torch.cuda.device(weight.device):
+        rc = _load().lutgemm_layer_weight_prep(weight.data_ptr(), s[0], s[1], s[2], s[3], Cout, Cin, kh, kw, quant.data_ptr(),
+                                               float(qmax), wmat.data_ptr(), wsum.data_ptr(), _stream_ptr(weight.device))
+    _check(rc, "layer_weight_prep")
+    return wmat, wsum
+
+
+def layer_cross_terms(wsum: torch.Tensor, Cin: int, H: int, W: int, kh: int, kw: int, stride: int, pad: int, dil: int):
+    """(sumw_t f32 [Ho*Wo, Cout], taps f32 [Ho*Wo]): per output position the weight-code sums over the taps inside
+    the image, and Cin times the number of those taps."""
+    Cout = wsum.shape[0]
+    Ho, Wo = _conv_out(H, W, kh, kw, stride, pad, dil)
+    sumw_t = torch.empty((Ho * Wo, Cout), dtype=torch.float32, device=wsum.device)
+    taps = torch.empty((Ho * Wo,), dtype=torch.float32, device=wsum.device)
+    with torch.cuda.device(wsum.device):
+        rc = _load().lutgemm_layer_cross_terms(wsum.data_ptr(), Cout, Cin, H, W, kh, kw, stride, pad, dil, sumw_t.data_ptr(),
+                                               taps.data_ptr(), _stream_ptr(wsum.device))
+    _check(rc, "layer_cross_terms")
+    return sumw_t, taps
+
+
+def layer_window_sum(img: torch.Tensor, kh: int, kw: int, stride: int, pad: int, dil: int) -> torch.Tensor:
+    """[B, H, W] f32 -> [B*Ho*Wo] f32: sum of the kernel window at every output position (zero padding)."""
+    _check_input(img, torch.float32, "image")
+    B, H, W = img.shape
+    Ho, Wo = _conv_out(H, W, kh, kw, stride, pad, dil)
+    box = torch.empty((B * Ho * Wo,), dtype=torch.float32, device=img.device)
+    with torch.cuda.device(img.device):
+        rc = _load().lutgemm_layer_window_sum(img.data_ptr(), B, H, W, kh, kw, stride, pad, dil, box.data_ptr(),
+                                              _stream_ptr(img.device))
+    _check(rc, "layer_window_sum")
+    return box
+
+
+def layer_window_sum_adjoint(gsum: torch.Tensor, H: int, W: int, kh: int, kw: int, stride: int, pad: int, dil: int):
+    """[B, Ho, Wo] f32 -> [B, H, W] f32: adjoint of `layer_window_sum`."""
+    _check_input(gsum, torch.float32, "grad_sum")
+    B = gsum.shape[0]
+    out = torch.empty((B, H, W), dtype=torch.float32, device=gsum.device)
+    with torch.cuda.device(gsum.device):
+        rc = _load().lutgemm_layer_window_sum_adjoint(gsum.data_ptr(), B, H, W, kh, kw, stride, pad, dil, out.data_ptr(),
+                                                      _stream_ptr(gsum.device))
+    _check(rc, "layer_window_sum_adjoint")
+    return out
+
+
+def layer_weight_grad(gwmat: torch.Tensor, tapg: torch.Tensor, weight: torch.Tensor, quant: torch.Tensor, qmax: float):
+    """Gradient w.r.t. the fp32 weight [Cout, Cin, kh, kw] (contiguous) from the gradient w.r.t. its codes
+    gwmat f32 [Cin*kh*kw, Cout] and the cross-term gradient tapg f32 [Cout, kh*kw]."""
+    _check_input(gwmat, torch.float32, "grad_codes")
+    _check_input(tapg, torch.float32, "tap_grad")
+    Cout, Cin, kh, kw = weight.shape
+    gw = torch.empty((Cout, Cin, kh, kw), dtype=torch.float32, device=weight.device)
+    s = weight.stride()
+    with torch.cuda.device(weight.device):
+        rc = _load().lutgemm_layer_weight_grad(gwmat.data_ptr(), tapg.data_ptr(), weight.data_ptr(), s[0], s[1], s[2], s[3],
+                                               Cout, Cin, kh, kw, quant.data_ptr(), float(qmax), gw.data_ptr(),
+                                               _stream_ptr(weight.device))
+    _check(rc, "layer_weight_grad")
+    return gw

@@ -135,9 +135,13 @@ const char *lutgemm_status_string(int status) {
     return "unknown status";
 }
 
+int lutgemm_set_tma(int on) {
+    lutgemm::slab_fwd_set_tma(on != 0);
+    return LUTGEMM_OK;
+}
+
 int lutgemm_set_handover(int on) {
     lutgemm::slab_tall_set_handover(on != 0);
-    lutgemm::slab_fwd_set_handover(on != 0);
     return LUTGEMM_OK;
 }
 
@@ -195,7 +199,7 @@ static int forward_impl(const uint8_t *a, const uint8_t *w, uint32_t *c, const u
         const int pitch = codes_pitch(M);
         if (scratch) {
             if (scratch_bytes < (size_t)pitch * K) return LUTGEMM_E_SCRATCH;
-            const int trc = lutgemm::transpose_codes(a, static_cast<uint8_t *>(scratch), M, K, pitch, conv, s);
+            const int trc = lutgemm::transpose_codes(a, static_cast<uint8_t *>(scratch), M, K, pitch, conv, bits, s);
             if (trc != LUTGEMM_OK) return trc;
             at = static_cast<const uint8_t *>(scratch);
         }
@@ -261,7 +265,7 @@ static int backward_impl(const float *gc, const uint8_t *a, const uint8_t *w, fl
         const uint8_t *at = codes_t;  // left by the forward pass (same layout), or made here
         if (pl.gw_slab && pl.gw_at_pitch && !at) {
             uint8_t *dst = static_cast<uint8_t *>(scratch) + pl.gw_at_offset;
-            const int trc = lutgemm::transpose_codes(a, dst, M, K, pl.gw_at_pitch, conv, s);
+            const int trc = lutgemm::transpose_codes(a, dst, M, K, pl.gw_at_pitch, conv, bits, s);
             if (trc != LUTGEMM_OK) return trc;
             at = dst;
         }
@@ -628,6 +632,68 @@ int lutgemm_conv2d_epilogue(const uint32_t *y, const float *box, const float *su
     if (sms <= 0) return LUTGEMM_E_CUDA;
     return lutgemm::conv_epilogue(y, box, sumw_t, taps, s_a, s_w, z_a, z_w, bias, out, M, L, Cout, sms,
                                   static_cast<cudaStream_t>(stream));
+}
+
+// ---- small kernels of the layer wiring -----------------------------------------------------------------------
+int lutgemm_layer_update_ranges(const float *act_lo, const float *act_hi, const float *w_lo, const float *w_hi,
+                                float *act_min, float *act_max, float *act_seen, float *w_min, float *w_max, float *w_seen,
+                                float keep, float momentum, float a_qmax, float w_qmax, float eps, float *quant,
+                                void *stream) {
+    if (!act_lo || !act_hi || !w_lo || !w_hi || !act_min || !act_max || !act_seen || !w_min || !w_max || !w_seen || !quant)
+        return LUTGEMM_E_BADARG;
+    return lutgemm::layer_update_ranges(act_lo, act_hi, w_lo, w_hi, act_min, act_max, act_seen, w_min, w_max, w_seen, keep,
+                                        momentum, a_qmax, w_qmax, eps, quant, static_cast<cudaStream_t>(stream));
+}
+
+int lutgemm_layer_weight_prep(const float *weight, long s_co, long s_c, long s_h, long s_w, int Cout, int Cin, int kh, int kw,
+                              const float *quant, float qmax, uint8_t *wmat, float *wsum, void *stream) {
+    if (!weight || !quant || !wmat || !wsum || Cout <= 0 || Cin <= 0 || kh <= 0 || kw <= 0 || kh * kw > 4096)
+        return LUTGEMM_E_BADARG;
+    return lutgemm::layer_weight_prep(weight, s_co, s_c, s_h, s_w, Cout, Cin, kh, kw, quant, qmax, wmat, wsum,
+                                      static_cast<cudaStream_t>(stream));
+}
+
+int lutgemm_layer_cross_terms(const float *wsum, int Cout, int Cin, int H, int W, int kh, int kw, int stride, int pad,
+                              int dil, float *sumw_t, float *taps, void *stream) {
+    lutgemm::ConvGeom g{};
+    const int rc = make_geom(1, Cin, H, W, kh, kw, stride, pad, dil, &g);
+    if (rc != LUTGEMM_OK) return rc;
+    if (!wsum || !sumw_t || !taps || Cout <= 0) return LUTGEMM_E_BADARG;
+    const int sms = current_num_sms();
+    if (sms <= 0) return LUTGEMM_E_CUDA;
+    return lutgemm::layer_cross_terms(wsum, Cout, g, sumw_t, taps, sms, static_cast<cudaStream_t>(stream));
+}
+
+int lutgemm_layer_window_sum(const float *img, int B, int H, int W, int kh, int kw, int stride, int pad, int dil,
+                             float *box, void *stream) {
+    lutgemm::ConvGeom g{};
+    const int rc = make_geom(B, 1, H, W, kh, kw, stride, pad, dil, &g);
+    if (rc != LUTGEMM_OK) return rc;
+    if (!img || !box) return LUTGEMM_E_BADARG;
+    const int sms = current_num_sms();
+    if (sms <= 0) return LUTGEMM_E_CUDA;
+    return lutgemm::layer_window_sum(img, g, box, sms, static_cast<cudaStream_t>(stream));
+}
+
+int lutgemm_layer_window_sum_adjoint(const float *gsum, int B, int H, int W, int kh, int kw, int stride, int pad, int dil,
+                                     float *out, void *stream) {
+    lutgemm::ConvGeom g{};
+    const int rc = make_geom(B, 1, H, W, kh, kw, stride, pad, dil, &g);
+    if (rc != LUTGEMM_OK) return rc;
+    if (!gsum || !out) return LUTGEMM_E_BADARG;
+    const int sms = current_num_sms();
+    if (sms <= 0) return LUTGEMM_E_CUDA;
+    return lutgemm::layer_window_sum_adjoint(gsum, g, out, sms, static_cast<cudaStream_t>(stream));
+}
+
+int lutgemm_layer_weight_grad(const float *gwmat, const float *tapg, const float *weight, long s_co, long s_c, long s_h,
+                              long s_w, int Cout, int Cin, int kh, int kw, const float *quant, float qmax, float *gw,
+                              void *stream) {
+    if (!gwmat || !tapg || !weight || !quant || !gw || Cout <= 0 || Cin <= 0 || kh <= 0 || kw <= 0) return LUTGEMM_E_BADARG;
+    const int sms = current_num_sms();
+    if (sms <= 0) return LUTGEMM_E_CUDA;
+    return lutgemm::layer_weight_grad_finish(gwmat, tapg, weight, s_co, s_c, s_h, s_w, Cout, Cin, kh, kw, quant, qmax, gw,
+                                             sms, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

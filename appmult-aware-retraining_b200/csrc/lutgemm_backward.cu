@@ -583,7 +583,7 @@ int backward_gw(const float *gc, const uint8_t *a, const uint8_t *w, float *gw, 
 // image the (channel, tap) of k and the (image, row, column) of the first m are decoded once per thread and m
 // advances incrementally; for a plain [M,K] matrix the byte loads of the 32 k of a block share sectors.
 __global__ void __launch_bounds__(1024) transpose_codes_kernel(const uint8_t *__restrict__ a, uint8_t *__restrict__ at,
-                                                               int M, int K, int pitch, const ConvGeom g) {
+                                                               int M, int K, int pitch, const ConvGeom g, uint32_t mask4) {
     const int k = blockIdx.y * 32 + threadIdx.y;
     const int m0 = (blockIdx.x * 32 + threadIdx.x) * 16;
     if (k >= K || m0 >= pitch) return;
@@ -605,14 +605,14 @@ __global__ void __launch_bounds__(1024) transpose_codes_kernel(const uint8_t *__
         for (int e = 0; e < 16; ++e)
             if (m0 + e < M) v[e >> 2] |= (uint32_t)a[(size_t)(m0 + e) * K + k] << (8 * (e & 3));
     }
-    *reinterpret_cast<uint4 *>(at + (size_t)k * pitch + m0) = make_uint4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<uint4 *>(at + (size_t)k * pitch + m0) = make_uint4(v[0] & mask4, v[1] & mask4, v[2] & mask4, v[3] & mask4);
 }
 
 // The same for a convolution whose output plane is a multiple of 16 positions and whose input plane fits
 // shared memory: one CTA stages the plane x[b,c,:,:] once (coalesced) and writes the kh*kw shifted copies of
 // it, 16 output positions per thread and store.
 __global__ void __launch_bounds__(256) transpose_codes_plane_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ at,
-                                                                    int pitch, const ConvGeom g) {
+                                                                    int pitch, const ConvGeom g, uint32_t mask4) {
     extern __shared__ __align__(16) uint8_t plane[];
     const int bc = blockIdx.x, b = bc / g.C, c = bc - b * g.C;
     const int HW = g.H * g.W, L = g.Ho * g.Wo, kk = g.kh * g.kw;
@@ -639,11 +639,13 @@ __global__ void __launch_bounds__(256) transpose_codes_plane_kernel(const uint8_
             if (++ow == g.Wo) { ow = 0; ++oh; }
         }
         *reinterpret_cast<uint4 *>(at + (size_t)(c * kk + tap) * pitch + (size_t)b * L + l0) =
-            make_uint4(v[0], v[1], v[2], v[3]);
+            make_uint4(v[0] & mask4, v[1] & mask4, v[2] & mask4, v[3] & mask4);
     }
 }
 
-int transpose_codes(const uint8_t *a, uint8_t *at, int M, int K, int pitch, const ConvGeom &conv, cudaStream_t stream) {
+int transpose_codes(const uint8_t *a, uint8_t *at, int M, int K, int pitch, const ConvGeom &conv, int bits,
+                    cudaStream_t stream) {
+    const uint32_t mask4 = ((1u << bits) - 1u) * 0x01010101u;  // codes are cut to `bits` bits on their way through
     // (small planes leave a CTA too little to do: they take the generic kernel)
     if (conv.enabled && (conv.Ho * conv.Wo) % 16 == 0 && conv.Ho * conv.Wo >= 256 && conv.H * conv.W <= 96 * 1024 &&
         (long)conv.B * conv.C <= 0x7fffffffL) {
@@ -652,12 +654,12 @@ int transpose_codes(const uint8_t *a, uint8_t *at, int M, int K, int pitch, cons
         if (smem > 48 * 1024 &&
             !cuda_ok(cudaFuncSetAttribute(transpose_codes_plane_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
             return LUTGEMM_E_CUDA;
-        transpose_codes_plane_kernel<<<conv.B * conv.C, 256, smem, stream>>>(a, at, pitch, conv);
+        transpose_codes_plane_kernel<<<conv.B * conv.C, 256, smem, stream>>>(a, at, pitch, conv, mask4);
         return launch_status();
     }
     const dim3 block(32, 32), grid((pitch / 16 + 31) / 32, (K + 31) / 32);
     if (grid.y > 65535u) return LUTGEMM_E_TOOLARGE;
-    transpose_codes_kernel<<<grid, block, 0, stream>>>(a, at, M, K, pitch, conv);
+    transpose_codes_kernel<<<grid, block, 0, stream>>>(a, at, M, K, pitch, conv, mask4);
     return launch_status();
 }
 

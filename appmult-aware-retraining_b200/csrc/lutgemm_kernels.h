@@ -31,6 +31,8 @@ int forward_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t
                  const ConvGeom &conv, const uint8_t *at, int at_pitch, const LayerEpilogue *epi, int num_sms,
                  cudaStream_t stream);
 
+// operand chunks of forward_slab by bulk-tensor copies (default) or by vector loads through registers
+void slab_fwd_set_tma(bool on);
 // number of K ranges forward_slab cuts a problem into when it is free to (1 = none; a fused epilogue needs 1)
 int slab_fwd_ksplits(int M, int K, int N, int num_sms);
 
@@ -75,15 +77,14 @@ int backward_gx_class(const float *gy, const uint8_t *x, const uint8_t *wmat, fl
 // taps * Cout is too short to amortise a slab build
 int backward_gx_bcast(const float *gy, const uint8_t *x, const uint8_t *wmat, float *gx, const int16_t *lut_ga, int bits,
                       int Cout, const PixelClass *classes, int nclasses, int num_sms, cudaStream_t stream);
-// hand-over between the warps of the tall gradient / forward slab kernels: per-buffer mbarriers (default) or one
-// CTA barrier per k
+// hand-over between the warps of the tall gradient kernels: per-buffer mbarriers (default) or one CTA barrier per k
 void slab_tall_set_handover(bool on);
-void slab_fwd_set_handover(bool on);
 
 
-// at[k][m] = a[m][k] (or the unfolded code image when conv.enabled); rows `pitch` bytes apart, pitch a multiple
-// of 16 and >= M, columns m >= M are written as 0
-int transpose_codes(const uint8_t *a, uint8_t *at, int M, int K, int pitch, const ConvGeom &conv, cudaStream_t stream);
+// at[k][m] = a[m][k] cut to `bits` bits (or the unfolded code image when conv.enabled); rows `pitch` bytes apart,
+// pitch a multiple of 16 and >= M, columns m >= M are written as 0
+int transpose_codes(const uint8_t *a, uint8_t *at, int M, int K, int pitch, const ConvGeom &conv, int bits,
+                    cudaStream_t stream);
 
 // quantisation prologue / epilogue of an approximate convolution layer (lutgemm_quant.cu); strides in elements
 int quantize_codes(const float *x, long sb, long sc, long sh, long sw, int B, int C, int H, int W, const float *scale,
@@ -94,6 +95,20 @@ int quantize_backward(const float *x, long sb, long sc, long sh, long sw, int B,
 int conv_epilogue(const uint32_t *y, const float *box, const float *sumw_t, const float *taps, const float *s_a,
                   const float *s_w, const float *z_a, const float *z_w, const float *bias, float *out, long M, int L,
                   int Cout, int num_sms, cudaStream_t stream);
+
+// small one-pass kernels of the layer wiring (lutgemm_layer_aux.cu); strides in elements, quant = {s_a, z_a, s_w, z_w}
+int layer_update_ranges(const float *act_lo, const float *act_hi, const float *w_lo, const float *w_hi, float *act_min,
+                        float *act_max, float *act_seen, float *w_min, float *w_max, float *w_seen, float keep,
+                        float momentum, float a_qmax, float w_qmax, float eps, float *quant, cudaStream_t stream);
+int layer_weight_prep(const float *weight, long s_co, long s_c, long s_h, long s_w, int Cout, int Cin, int kh, int kw,
+                      const float *quant, float qmax, uint8_t *wmat, float *wsum, cudaStream_t stream);
+int layer_cross_terms(const float *wsum, int Cout, const ConvGeom &g, float *sumw_t, float *taps, int num_sms,
+                      cudaStream_t stream);
+int layer_window_sum(const float *img, const ConvGeom &g, float *box, int num_sms, cudaStream_t stream);
+int layer_window_sum_adjoint(const float *gsum, const ConvGeom &g, float *out, int num_sms, cudaStream_t stream);
+int layer_weight_grad_finish(const float *gwmat, const float *tapg, const float *weight, long s_co, long s_c, long s_h,
+                             long s_w, int Cout, int Cin, int kh, int kw, const float *quant, float qmax, float *gw,
+                             int num_sms, cudaStream_t stream);
 
 // number of slabs the weight-gradient kernel splits M into (1 = no scratch needed)
 int gw_num_splits(int bits, int M, int K, int N, int num_sms);

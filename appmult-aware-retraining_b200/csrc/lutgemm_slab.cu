@@ -14,12 +14,9 @@
 // shared-memory wavefront instead of ~11.  The build reads the table transposed and paired ([w][x],
 // codes x and x + 2^b/2 in one word) with conflict-free 32-bit loads and writes slab rows (stride 34
 // words) with conflict-free 64-bit stores: 2^b * 2 wavefronts per k against 512 for the use phase.
-// Two slab buffers: slab k+1 is built while slab k is read.  The warps hand the buffers to each other through
-// mbarriers (per buffer a "full" barrier - all 16 warps have built their part - and an "empty" barrier - all
-// have finished reading it; one arrival per warp): a warp reads half of its rows of slab k, then, once slab
-// k-1 has been released, builds its part of slab k+1 and reads the other half, so each wait has half a read
-// phase of slack and the warps drift instead of lining up behind one CTA barrier per k.  Every wait is bounded
-// (lutgemm_waits.cuh).
+// Two slab buffers: slab k+1 is built while slab k is read, one CTA barrier per k.  (Handing the buffers over
+// through per-buffer mbarriers, as the gradient kernels do, was measured SLOWER here - 11.5 against 10.7 ms at
+// 8 bits, 9.7 against 8.9 ms at 7 bits for 4096^3 - the forward's read phase per k is half as long as theirs.)
 // The two halves of a slab word go to the accumulators as  S += word,  H += word >> 16 ; at the end
 // sum(lo) = S - (H << 16) (mod 2^32) and sum(hi) = H.
 // Work items are (tile, K split); splits of one tile are combined with integer atomics, which are
@@ -28,10 +25,17 @@
 // that copy is the uint8 im2col, made once) or, without a workspace, straight from a[m][k] - with
 // conv.enabled gathered from the NCHW code image on the fly (implicit im2col) - and transposed byte-wise
 // on their way into shared memory.
+// Operand delivery with a workspace: the k chunks of at[k][m] (two boxes of 16 k x 256 rows) and of w[k][n] (one box
+// of 16 k x 64 columns) are fetched by one elected thread with tiled bulk-tensor copies (TMA) straight into the
+// stage the kernel reads, completion counted on an mbarrier that every thread waits on (bounded) before the first
+// use of the chunk; the transposition kernel has already cut the activation codes to b bits, the weight codes are
+// cut when the build extracts them.  Without a workspace, or when w breaks a TMA alignment rule, the chunks go
+// through registers (16-byte vector loads) as before.
 // The gradient kernels built on the same idea are in lutgemm_slab_grad_tall.cu and lutgemm_slab_grad.cu.
 // Replaces ApproxGemmForwardKernel, self_ops/src/approx_gemm_forward.cu:37-229.
 #include "lutgemm_common.cuh"
 #include "lutgemm_kernels.h"
+#include "lutgemm_tma.cuh"
 #include "lutgemm_waits.cuh"
 
 namespace lutgemm {
@@ -47,12 +51,13 @@ struct Cfg {
     static constexpr int CT = 64;               // columns per CTA tile: 2 per lane
     static constexpr int KC = 16;               // k per operand stage
     static constexpr int U_STRIDE = 34;         // words per slab row (32 + 2 pad: 8-byte aligned rows)
-    static constexpr int TT_BYTES = Q * TT_STRIDE * 4;
+    static constexpr int TT_BYTES = (Q * TT_STRIDE * 4 + 127) & ~127;  // the stages behind it are TMA destinations
     static constexpr int U_BYTES = Q * U_STRIDE * 4;
-    static constexpr int RC_STAGE = KC * RT;
-    static constexpr int CC_STAGE = KC * CT;
+    static constexpr int RC_STAGE = KC * RT;   // [half][kk][256]: two boxes of 16 k x 256 rows
+    static constexpr int CC_STAGE = KC * CT;   // [kk][64]
     static constexpr int OFF_BAR = TT_BYTES + 2 * U_BYTES + 2 * RC_STAGE + 2 * CC_STAGE;
-    static constexpr int SMEM = OFF_BAR + 4 * 8 + 16;  // four mbarriers and the abort word
+    static constexpr int SMEM = OFF_BAR + 2 * 8 + 16;  // one mbarrier per stage and the abort word
+    static_assert(U_BYTES % 128 == 0 && RC_STAGE % 128 == 0 && CC_STAGE % 128 == 0, "TMA destinations are 128-byte aligned");
     static constexpr int NSETS = HALF > 32 ? HALF / 32 : 1;
 };
 
@@ -67,15 +72,20 @@ struct Args {
     ConvGeom conv;
     const uint8_t *at;  // optional: the activation codes transposed, at[k][m], rows at_pitch bytes apart
     int at_pitch;       // a multiple of 16; columns m >= M hold 0
-    int *error_word;    // device error word of the bounded waits
     LayerEpilogue epi;  // epi.out != nullptr: the de-quantised fp32 layer output is stored instead of c
+    int *error_word;    // device error word of the bounded waits (TMA instantiation)
 };
+
+// byte offset of activation code (kk, row) inside a row-code stage
+__device__ __forceinline__ int rc_off(int kk, int row) { return (row >> 8) * (16 * 256) + kk * 256 + (row & 255); }
 
 // USE_AT: the activation codes come from the transposed workspace copy (p.at); the other instantiation keeps
 // the direct / implicit-im2col fetch, so neither carries the other's registers.
-// HANDOVER: per-buffer mbarriers (see the file comment) instead of one CTA barrier per k.
-template <int BITS, bool USE_AT, bool HANDOVER>
-__global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p) {
+// TMA (with USE_AT): operand chunks by bulk-tensor copies (map_at over at[K][pitch], map_w over w[K][N]).
+template <int BITS, bool USE_AT, bool TMA>
+__global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p, const __grid_constant__ CUtensorMap map_at,
+                                                          const __grid_constant__ CUtensorMap map_w) {
+    static_assert(!TMA || USE_AT, "bulk-tensor operand loads read the transposed copy");
     using C = Cfg<BITS>;
     constexpr int Q = C::Q, HALF = C::HALF, TTS = C::TT_STRIDE, RT = C::RT, CT = C::CT, KC = C::KC;
     constexpr int US = C::U_STRIDE, THREADS = C::THREADS, NSETS = C::NSETS;
@@ -83,15 +93,21 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p) {
     constexpr int COL = lut_col_num(BITS);
     const int M = p.M, K = p.K, N = p.N;
 
-    extern __shared__ __align__(16) uint8_t smem[];
+    extern __shared__ __align__(128) uint8_t smem[];
     uint8_t *rc_s = smem + C::TT_BYTES + 2 * C::U_BYTES;
     uint8_t *cc_s = rc_s + 2 * C::RC_STAGE;
     const uint32_t tt_addr = smem_u32(smem);
     const uint32_t u_addr = smem_u32(smem + C::TT_BYTES);
-    const uint32_t bar_full = smem_u32(smem + C::OFF_BAR), bar_empty = bar_full + 16;
-    volatile int *abort_word = reinterpret_cast<volatile int *>(smem + C::OFF_BAR + 32);
     const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
-    if (tid == 0) *abort_word = 0;
+    const uint32_t bar_stage = smem_u32(smem + C::OFF_BAR);  // TMA: one barrier per operand stage
+    volatile int *abort_word = reinterpret_cast<volatile int *>(smem + C::OFF_BAR + 16);
+    uint32_t stage_phase = 0;                                 // TMA: bit s = parity of the next completion of stage s
+    if (TMA && tid == 0) {
+        *abort_word = 0;
+        mbar_init(bar_stage, 1);
+        mbar_init(bar_stage + 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");  // visible to the copy engine
+    }
 
     // ---- stage the table transposed and paired: tt[w][i] = { LUT[i][w], LUT[i + HALF][w] } ---------------
     {
@@ -135,11 +151,11 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p) {
         const uint32_t tr[4] = {prc.x & MASK4, prc.y & MASK4, prc.z & MASK4, prc.w & MASK4};
         uint8_t *rs = rc_s + stage * C::RC_STAGE;
         if (USE_AT) {
-            *reinterpret_cast<uint4 *>(rs + (tid / (RT / 16)) * RT + (tid % (RT / 16)) * 16) =
+            *reinterpret_cast<uint4 *>(rs + rc_off(tid / (RT / 16), (tid % (RT / 16)) * 16)) =
                 make_uint4(tr[0], tr[1], tr[2], tr[3]);
         } else {
 #pragma unroll
-            for (int q = 0; q < 16; ++q) rs[q * RT + tid] = (uint8_t)(tr[q >> 2] >> (8 * (q & 3)));
+            for (int q = 0; q < 16; ++q) rs[rc_off(q, tid)] = (uint8_t)(tr[q >> 2] >> (8 * (q & 3)));
         }
         if (tid < KC * CT / 16)
             *reinterpret_cast<uint4 *>(cc_s + stage * C::CC_STAGE + (tid / (CT / 16)) * CT + (tid % (CT / 16)) * 16) =
@@ -149,7 +165,9 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p) {
     auto build = [&](int buf, int stage, int kk) {
         const uint32_t cw = *reinterpret_cast<const uint32_t *>(cc_s + stage * C::CC_STAGE + kk * CT + wp * 4);
         const uint32_t ub = u_addr + buf * C::U_BYTES + wp * 8;  // this warp's four columns: words 2wp and 2wp+1
-        const uint32_t y0 = byte_of(cw, 0), y1 = byte_of(cw, 1), y2 = byte_of(cw, 2), y3 = byte_of(cw, 3);
+        // (chunks that arrive by bulk copy have not been through the masking store: cut the codes to BITS bits here)
+        const uint32_t cwm = TMA ? (cw & MASK4) : cw;
+        const uint32_t y0 = byte_of(cwm, 0), y1 = byte_of(cwm, 1), y2 = byte_of(cwm, 2), y3 = byte_of(cwm, 3);
 #pragma unroll
         for (int j = 0; j < NSETS; ++j) {
             const int i = lane + 32 * j;
@@ -167,8 +185,24 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p) {
         }
     };
 
+    // TMA: thread 0 starts the three copies of a chunk into `stage` (every thread is past a CTA barrier after its last
+    // read of that stage); all threads wait for them before the chunk's first use
+    auto tma_issue = [&](int m0, int n0, int chunk, int stage) {
+        if (tid != 0) return;
+        tma_fence_before_load();
+        const uint32_t bar = bar_stage + 8 * stage;
+        tma_expect_bytes(bar, C::RC_STAGE + C::CC_STAGE);
+        const uint32_t rs = smem_u32(rc_s + stage * C::RC_STAGE), cs = smem_u32(cc_s + stage * C::CC_STAGE);
+        tma_load_2d(rs, &map_at, m0, chunk * KC, bar);
+        tma_load_2d(rs + KC * 256, &map_at, m0 + 256, chunk * KC, bar);
+        tma_load_2d(cs, &map_w, n0, chunk * KC, bar);
+    };
+    auto tma_wait = [&](int stage) {
+        mbar_wait(bar_stage + 8 * stage, (stage_phase >> stage) & 1u, 21 + stage, abort_word, p.error_word);
+        stage_phase ^= 1u << stage;
+    };
+
     const int items = p.tiles_r * p.tiles_c * p.ksplits;
-    bool first_item = true;
     for (int item = blockIdx.x; item < items; item += gridDim.x) {
         const int tile = item / p.ksplits;
         const int kbeg = (item % p.ksplits) * p.k_per_split, kend = min(K, kbeg + p.k_per_split);
@@ -178,76 +212,46 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p) {
 #pragma unroll
         for (int r = 0; r < 32; ++r) acc[r][0] = acc[r][1] = 0u;
 
-        fetch_chunk(m0, n0, kbeg / KC);
-        __syncthreads();  // previous item (or the table staging) is done with every buffer
-        store_chunk((kbeg / KC) & 1);
-        if (HANDOVER && tid == 0) {
-            // fresh barriers for this item: phases restart at 0 (nobody is waiting or arriving here)
-#pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                if (!first_item) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar_full + 8 * b) : "memory");
-                mbar_init(bar_full + 8 * b, 16);
-            }
-        }
-        first_item = false;
-        __syncthreads();
-        build(kbeg & 1, (kbeg / KC) & 1, 0);
-        if (HANDOVER) {
-            __syncwarp();
-            // slab kbeg is complete once every warp has arrived; the other buffer starts out released
-            if (lane == 0) {
-                mbar_arrive(bar_full + 8 * (kbeg & 1));
-                mbar_arrive(bar_empty + 8 * ((kbeg & 1) ^ 1));
-            }
+        if (TMA) {
+            __syncthreads();  // previous item (or the table staging and barrier set-up) is done with every buffer
+            tma_issue(m0, n0, kbeg / KC, (kbeg / KC) & 1);
+            tma_wait((kbeg / KC) & 1);
         } else {
+            fetch_chunk(m0, n0, kbeg / KC);
+            __syncthreads();  // previous item (or the table staging) is done with every buffer
+            store_chunk((kbeg / KC) & 1);
             __syncthreads();
         }
+        build(kbeg & 1, (kbeg / KC) & 1, 0);
+        __syncthreads();
 
-        // use slab k: slab row a[m,k], two columns per lane, for rows [rb, re) of this warp's 32 rows
-        auto use_rows = [&](int k, int stage, int kk, int rb, int re) {
-            const uint4 *rp = reinterpret_cast<const uint4 *>(rc_s + stage * C::RC_STAGE + kk * RT + wp * 32);
-            const uint4 q0 = rp[rb / 16];
-            const uint32_t rv[4] = {q0.x, q0.y, q0.z, q0.w};
+        for (int k = kbeg; k < kend; ++k) {
+            const int chunk = k / KC, kk = k % KC, stage = chunk & 1;
+            const bool have_next_chunk = (chunk + 1) * KC < kend;
+            if (TMA) {
+                // the other stage was last read before the barrier that ended the previous k: refill it now, and
+                // make sure it has landed before the last k of this chunk builds the next chunk's first slab
+                if (kk == 0 && have_next_chunk) tma_issue(m0, n0, chunk + 1, stage ^ 1);
+                if (kk == KC - 1 && have_next_chunk) tma_wait(stage ^ 1);
+            } else if (kk == 0 && have_next_chunk) fetch_chunk(m0, n0, chunk + 1);
+            if (k + 1 < kend) build((k + 1) & 1, ((k + 1) / KC) & 1, (k + 1) % KC);
+
+            // use slab k: slab row a[m,k], two columns per lane, for this warp's 32 rows
+            const uint4 *rp = reinterpret_cast<const uint4 *>(rc_s + stage * C::RC_STAGE + rc_off(kk, wp * 32));
+            const uint4 q0 = rp[0], q1 = rp[1];
+            const uint32_t rv[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
             const uint32_t ub = u_addr + (k & 1) * C::U_BYTES + lane * 4;
 #pragma unroll
             for (int r = 0; r < 32; ++r) {
-                if (r < rb || r >= re) continue;
                 // slab row address = base + 136 * code in one integer dot-product instruction
-                const uint32_t addr = byte_scaled_add<US * 4>(rv[(r >> 2) & 3], r & 3, ub);
+                const uint32_t addr = byte_scaled_add<US * 4>(rv[r >> 2], r & 3, ub);
                 uint32_t word;
                 asm volatile("ld.shared.u32 %0, [%1];" : "=r"(word) : "r"(addr));
                 acc[r][0] += word;
                 acc[r][1] += word >> 16;
             }
-        };
-
-        for (int k = kbeg; k < kend; ++k) {
-            const int chunk = k / KC, kk = k % KC, stage = chunk & 1;
-            const bool have_next_chunk = (chunk + 1) * KC < kend;
-            if (kk == 0 && have_next_chunk) fetch_chunk(m0, n0, chunk + 1);
-            if (HANDOVER) {
-                // phase of either barrier that belongs to this step: its (kl / 2)-th since the item began
-                const int b = k & 1;
-                const uint32_t par = ((k - kbeg) >> 1) & 1;
-                mbar_wait(bar_full + 8 * b, par, 11 + b, abort_word, p.error_word);         // slab k is complete
-                use_rows(k, stage, kk, 0, 16);
-                mbar_wait(bar_empty + 8 * (b ^ 1), par, 13 + b, abort_word, p.error_word);  // slab k-1 is released
-                if (k + 1 < kend) {
-                    build((k + 1) & 1, ((k + 1) / KC) & 1, (k + 1) % KC);
-                    if (kk == KC - 2 && have_next_chunk) store_chunk(stage ^ 1);
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_full + 8 * (b ^ 1));
-                }
-                use_rows(k, stage, kk, 16, 32);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_empty + 8 * b);
-            } else {
-                if (k + 1 < kend) build((k + 1) & 1, ((k + 1) / KC) & 1, (k + 1) % KC);
-                use_rows(k, stage, kk, 0, 16);
-                use_rows(k, stage, kk, 16, 32);
-                if (kk == KC - 2 && have_next_chunk) store_chunk(stage ^ 1);
-                __syncthreads();
-            }
+            if (!TMA && kk == KC - 2 && have_next_chunk) store_chunk(stage ^ 1);
+            __syncthreads();
         }
 
         const int n = n0 + 2 * lane;
@@ -284,6 +288,9 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p) {
 
 }  // namespace sf
 
+static bool g_fwd_tma = true;  // bulk-tensor operand loads (false: 16-byte vector loads through registers)
+void slab_fwd_set_tma(bool on) { g_fwd_tma = on; }
+
 // the K split that best fills the last wave of the persistent grid (1 = every tile sums its whole K range)
 int slab_fwd_ksplits(int M, int K, int N, int num_sms) {
     using C = sf::Cfg<8>;  // tile geometry does not depend on the bit-width
@@ -302,16 +309,21 @@ int slab_fwd_ksplits(int M, int K, int N, int num_sms) {
     return ksplits;
 }
 
-static bool g_fwd_handover = false;  // per-buffer mbarrier hand-over; measured slower than one CTA barrier per k here
-void slab_fwd_set_handover(bool on) { g_fwd_handover = on; }
-
 template <int BITS>
 static int launch_fwd_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, const uint16_t *lut, int M, int K, int N,
                            const ConvGeom &conv, const uint8_t *at, int at_pitch, const LayerEpilogue *epi, int num_sms,
                            cudaStream_t stream) {
     using C = sf::Cfg<BITS>;
-    auto kern = at ? (g_fwd_handover ? sf::slab_fwd_kernel<BITS, true, true> : sf::slab_fwd_kernel<BITS, true, false>)
-                   : (g_fwd_handover ? sf::slab_fwd_kernel<BITS, false, true> : sf::slab_fwd_kernel<BITS, false, false>);
+    // operand chunks by bulk-tensor copies where the transposed copy exists and w keeps the copy engine's alignment
+    // rules (base and row pitch multiples of 16 bytes); otherwise through registers
+    CUtensorMap map_at{}, map_w{};
+    const bool tma = at && g_fwd_tma && N % 16 == 0 &&
+                     make_tensor_map_u8_2d(&map_at, at, (unsigned long long)at_pitch, (unsigned long long)K,
+                                           (unsigned long long)at_pitch, 256, C::KC) &&
+                     make_tensor_map_u8_2d(&map_w, w, (unsigned long long)N, (unsigned long long)K, (unsigned long long)N,
+                                           C::CT, C::KC);
+    auto kern = tma ? sf::slab_fwd_kernel<BITS, true, true>
+                    : at ? sf::slab_fwd_kernel<BITS, true, false> : sf::slab_fwd_kernel<BITS, false, false>;
     if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM)))
         return LUTGEMM_E_CUDA;
     sf::Args p{};
@@ -319,9 +331,9 @@ static int launch_fwd_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, cons
     p.conv = conv;
     p.at = at;
     p.at_pitch = at_pitch;
+    if (epi) p.epi = *epi;
     p.error_word = device_error_word();
     if (!p.error_word) return LUTGEMM_E_CUDA;
-    if (epi) p.epi = *epi;
     p.tiles_r = (M + C::RT - 1) / C::RT;
     p.tiles_c = (N + C::CT - 1) / C::CT;
     const long tiles = (long)p.tiles_r * p.tiles_c;
@@ -337,7 +349,7 @@ static int launch_fwd_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, cons
     p.vec_a = !conv.enabled && (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(a) & 15) == 0);
     p.vec_w = (N % 16 == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
     p.vec_c = (N % 2 == 0) && ((reinterpret_cast<uintptr_t>(c) & 7) == 0);
-    kern<<<grid, C::THREADS, C::SMEM, stream>>>(p);
+    kern<<<grid, C::THREADS, C::SMEM, stream>>>(p, map_at, map_w);
     return launch_status();
 }
 

@@ -91,16 +91,14 @@ struct Args {
 // USE_AT (grad_w only): the row codes come from the transposed copy p.at; the other instantiation keeps the
 // direct / implicit-im2col fetch, so neither carries the other's registers.
 // HANDOVER: per-buffer mbarriers (see the file comment) instead of one CTA barrier per k.
-template <int BITS, int MODE, int RW, bool USE_AT, bool HANDOVER, int PF_ = 0>
+template <int BITS, int MODE, int RW, bool USE_AT, bool HANDOVER>
 __global__ void __launch_bounds__(512, 1) slab_grad_tall_kernel(const Args p) {
     using C = Cfg<BITS, RW>;
     constexpr int WARPS = C::WARPS;
     constexpr int Q = C::Q, HALF = C::HALF, TTS = C::TT_STRIDE, RT = C::RT, CT = C::CT, KC = C::KC, SC = C::SC;
     constexpr int US = C::U_STRIDE, PS = C::P_STRIDE, THREADS = C::THREADS, NSEG = C::NSEG, RCL = C::RC_LOADS;
     constexpr int HALVES = KC / SC;  // shared-memory stages per fetched group of 16 k
-    // slab reads in flight ahead of their use: a short row range per warp leaves registers for a deeper pipeline,
-    // and needs it (its read phases are too short to hide shared-memory latency behind other warps)
-    constexpr int PF = PF_ ? PF_ : (RW <= 36 ? 8 : 4);
+    constexpr int PF = 4;            // slab reads in flight ahead of their use (2 to 16 measured alike)
     constexpr uint32_t MASK4 = (Q - 1) * 0x01010101u;
     constexpr int COL = lut_col_num(BITS);
     static_assert(MODE != kGw || USE_AT || RT % THREADS == 0, "grad_w without a transposed copy: whole rows per thread");
@@ -495,8 +493,6 @@ int slab_tall_row_blocks(int rdim) { return (rdim + kSlabTallRows - 1) / kSlabTa
 namespace {
 
 bool g_tall_handover = true;  // per-buffer mbarrier hand-over (false: one CTA barrier per k)
-int g_dbg_force_rw = 0;
-int g_dbg_pf = 0;
 
 
 template <int BITS, int MODE, int RW>
@@ -509,13 +505,6 @@ int launch_slab_grad_tall(sgt::Args p, float *out, float *scratch, int num_sms, 
                              : sgt::slab_grad_tall_kernel<BITS, MODE, RW, MODE == sgt::kGw, false>)
                        : (ho ? sgt::slab_grad_tall_kernel<BITS, MODE, RW, false, true>
                              : sgt::slab_grad_tall_kernel<BITS, MODE, RW, false, false>);
-    if constexpr (MODE == sgt::kGx && BITS >= 7 && (RW == 36 || RW == 64)) {
-        if (g_dbg_pf == 2) kern = sgt::slab_grad_tall_kernel<BITS, MODE, RW, false, true, 2>;
-        if (g_dbg_pf == 4) kern = sgt::slab_grad_tall_kernel<BITS, MODE, RW, false, true, 4>;
-        if (g_dbg_pf == 8) kern = sgt::slab_grad_tall_kernel<BITS, MODE, RW, false, true, 8>;
-        if (g_dbg_pf == 12) kern = sgt::slab_grad_tall_kernel<BITS, MODE, RW, false, true, 12>;
-        if (g_dbg_pf == 16) kern = sgt::slab_grad_tall_kernel<BITS, MODE, RW, false, true, 16>;
-    }
     if (!cuda_ok(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM)))
         return LUTGEMM_E_CUDA;
     p.error_word = device_error_word();
@@ -594,7 +583,6 @@ int launch_gx_class(const float *gy, const uint8_t *x, const uint8_t *wmat, floa
     int rw = 64;
     for (int cand : {36, 32})
         if (gx_step_cost(BITS, p.RDIM, cand) < gx_step_cost(BITS, p.RDIM, rw)) rw = cand;
-    if (g_dbg_force_rw) rw = g_dbg_force_rw;
     int rc;
     if (rw == 36) rc = launch_slab_grad_tall<BITS, sgt::kGx, 36>(p, gx, scratch, num_sms, stream);
     else if (rw == 32) rc = launch_slab_grad_tall<BITS, sgt::kGx, 32>(p, gx, scratch, num_sms, stream);
@@ -609,7 +597,6 @@ int launch_gx_class(const float *gy, const uint8_t *x, const uint8_t *wmat, floa
 }  // namespace
 
 void slab_tall_set_handover(bool on) { g_tall_handover = on; }
-extern "C" void lutgemm_dbg_force_rw(int rw) { g_dbg_force_rw = rw % 100; g_dbg_pf = rw / 100; }
 
 int backward_gw_slab_tall(const float *gc, const uint8_t *a, const uint8_t *w, float *gw, const int16_t *lut_gw,
                           const float *lut_f32, int bits, int M, int K, int N, const ConvGeom &conv, float *scratch,
@@ -640,7 +627,6 @@ size_t gx_class_scratch_bytes(int bits, int Cout, const PixelClass &px, int B) {
     int rw = 64;
     for (int cand : {36, 32})
         if (gx_step_cost(bits, rdim, cand) < gx_step_cost(bits, rdim, rw)) rw = cand;
-    if (g_dbg_force_rw) rw = g_dbg_force_rw;
     const long tiles_r = (rdim + 16L * rw - 1) / (16L * rw);
     return tiles_r > 1 ? (size_t)tiles_r * px.C * ((size_t)B * px.Hc * px.Wc) * sizeof(float) : 0;
 }

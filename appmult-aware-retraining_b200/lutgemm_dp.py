@@ -114,7 +114,11 @@ class OverlappedGradReducer:
             self._launch(b)
 
     def _view_of(self, p):
+        # a view with the parameter's own (dense) strides, e.g. channels-last convolution weights, so that autograd
+        # accumulates into it without a layout mismatch
         off = self._offsets[p]
+        if p.dim() == 4 and not p.is_contiguous() and p.is_contiguous(memory_format=torch.channels_last):
+            return self.flat.as_strided(p.shape, p.stride(), off)
         return self.flat[off:off + p.numel()].view(p.shape)
 
     def _launch(self, b):

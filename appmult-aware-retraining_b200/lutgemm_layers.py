@@ -46,7 +46,8 @@ def _tap_slices(geom):
 
 
 def _window_sum(img, geom):
-    """[B, H, W] -> [B, Ho, Wo]: sum of the kernel window at every output position (zero padding)."""
+    """[B, H, W] -> [B, Ho, Wo]: sum of the kernel window at every output position (zero padding).  PyTorch
+    statement of what `approx_ops.layer_window_sum` computes in one kernel; the tests hold the kernel against it."""
     pad = geom[5]
     padded = F.pad(img, (pad, pad, pad, pad))
     out = None
@@ -97,13 +98,11 @@ class _AppConvLayer(torch.autograd.Function):
         if not (x.is_contiguous() or x.is_contiguous(memory_format=torch.channels_last)):
             x = x.contiguous()
         codes, chansum = approx_ops.quantize_activations(x, s_a, z_a, a_qmax)
-        qw = torch.clamp(torch.round(weight / s_w - z_w), 0.0, w_qmax)
-        wmat = qw.reshape(Cout, -1).t().to(torch.uint8).contiguous()
-        geom = (H, W, kh, kw, stride, padding, dilation)
-        valid = _valid_taps(geom, x.device)                                   # [kh*kw, L]
-        box = _window_sum(chansum, geom).reshape(M)
-        sumw_t = (valid.t() @ qw.sum(dim=1).reshape(Cout, kh * kw).t()).contiguous()  # [L, Cout]
-        taps = valid.sum(dim=0) * float(Cin)
+        # weight codes as the [K, Cout] matrix of the LUT kernels + their per-tap sums; the two z_a cross terms per
+        # output position; the window sums of the channel-summed activation codes (one small kernel each)
+        wmat, wsum = approx_ops.layer_weight_prep(weight, quant, w_qmax)
+        sumw_t, taps = approx_ops.layer_cross_terms(wsum, Cin, H, W, kh, kw, stride, padding, dilation)
+        box = approx_ops.layer_window_sum(chansum, kh, kw, stride, padding, dilation)
         # one kernel: LUT convolution with the de-quantisation applied to the sums in registers
         out, codes_t = approx_ops.approx_conv2d_forward_layer(codes, wmat, _ops_state.lut_appmult, kh, kw, stride, padding,
                                                               dilation, box, sumw_t, taps, s_a, s_w, z_a, z_w, bias)
@@ -132,15 +131,14 @@ class _AppConvLayer(torch.autograd.Function):
         gx = gw = gb = None
         if need_x:
             # cross term z_w * box(q_a): its adjoint spreads the channel sum of grad_out over each window
-            box_t = _window_sum_adjoint(gy.sum(dim=1).view(B, Ho, Wo), geom)
+            box_t = approx_ops.layer_window_sum_adjoint(gy.sum(dim=1).view(B, Ho, Wo), H, W, kh, kw, stride, padding, dilation)
             gx = approx_ops.quantize_activations_backward(x, s_a, z_a, a_qmax, gcodes, box_t, s_w, z_w)
         if need_w:
-            # cross term z_a * sum_w(q_w): every input channel of a tap sees the same sum of grad_out
+            # cross term z_a * sum_w(q_w): every input channel of a tap sees the same sum of grad_out; then clamp
+            # mask and activation scale in one pass
             gsum_b = gy.view(B, L, Cout).sum(dim=0)                                          # [L, Cout]
-            tap_grad = (_valid_taps(geom, gy.device) @ gsum_b).t().reshape(Cout, 1, kh, kw)
-            g_qw = gwmat.t().reshape(weight.shape) + z_a * tap_grad
-            q = torch.round(weight / s_w - z_w)
-            gw = torch.where((q >= 0) & (q <= w_qmax), s_a * g_qw, torch.zeros_like(g_qw))
+            tap_grad = (_valid_taps(geom, gy.device) @ gsum_b).t().contiguous()              # [Cout, kh*kw]
+            gw = approx_ops.layer_weight_grad(gwmat, tap_grad, weight, quant, w_qmax)
         if has_bias and ctx.needs_input_grad[2]:
             gb = gy.sum(dim=0)
         return gx, gw, gb, None, None, None, None, None, None
@@ -163,10 +161,9 @@ class _AppLinearLayer(torch.autograd.Function):
         # rows as the channel dimension of a one-row image: the kernel's 32 x 32 tiles are then all payload
         codes, _ = approx_ops.quantize_activations(x2.view(1, M, 1, K), s_a, z_a, a_qmax, want_chansum=False)
         codes = codes.view(M, K)
-        qw = torch.clamp(torch.round(weight / s_w - z_w), 0.0, w_qmax)
-        wmat = qw.t().to(torch.uint8).contiguous()
+        wmat, wsum = approx_ops.layer_weight_prep(weight.view(N, K, 1, 1), quant, w_qmax)  # [K, N] codes, [N, 1] sums
         box = codes.sum(dim=1, dtype=torch.float32)
-        sumw_t = qw.sum(dim=1).view(1, N).contiguous()
+        sumw_t = wsum.view(1, N)
         taps = torch.full((1,), float(K), device=x2.device)
         out, codes_t = approx_ops.approx_gemm_forward_layer(codes, wmat, _ops_state.lut_appmult, box, sumw_t, taps, s_a, s_w,
                                                             z_a, z_w, bias)
@@ -194,9 +191,9 @@ class _AppLinearLayer(torch.autograd.Function):
             gx = approx_ops.quantize_activations_backward(x2.view(1, M, 1, K), s_a, z_a, a_qmax, ga.view(1, M, 1, K),
                                                           None, s_w, z_w).view(M, K)
         if need_w:
-            g_qw = gw.t() + z_a * gy.sum(dim=0).unsqueeze(1)  # cross term z_a * colsum(q_w)
-            q = torch.round(weight / s_w - z_w)
-            gwt = torch.where((q >= 0) & (q <= w_qmax), s_a * g_qw, torch.zeros_like(g_qw))
+            # cross term z_a * colsum(q_w), clamp mask and activation scale in one pass
+            gwt = approx_ops.layer_weight_grad(gw, gy.sum(dim=0).view(-1, 1).contiguous(), weight.view(-1, K, 1, 1), quant,
+                                               w_qmax).view(weight.shape)
         if has_bias and ctx.needs_input_grad[2]:
             gb = gy.sum(dim=0)
         return gx, gwt, gb, None, None, None
@@ -211,6 +208,9 @@ class _MinMax(nn.Module):
         self.register_buffer("min_val", torch.zeros(1))
         self.register_buffer("max_val", torch.zeros(1))
         self.register_buffer("seen", torch.zeros(1))
+
+    def state(self):
+        return self.min_val, self.max_val, self.seen
 
     @torch.no_grad()
     def update(self, x: torch.Tensor) -> None:
@@ -234,13 +234,24 @@ class _AppQuant(nn.Module):
         self.weight_range = _MinMax(momentum=None)
         self.a_qmax = float((1 << a_bits) - 1)
         self.w_qmax = float((1 << w_bits) - 1)
-        for name in ("activation_scale", "weight_scale"):
-            self.register_buffer(name, torch.ones(1))
-        for name in ("activation_zp_neg", "weight_zp_neg"):
-            self.register_buffer(name, torch.zeros(1))
+        # {activation scale, activation zero point, weight scale, weight zero point}: one buffer, so that the kernels
+        # read all four from one place; the names below are views into it
+        self.register_buffer("quant", torch.tensor([1.0, 0.0, 1.0, 0.0]))
 
-    def _refresh(self, x: torch.Tensor, w: torch.Tensor) -> None:
+    activation_scale = property(lambda self: self.quant[0:1])
+    activation_zp_neg = property(lambda self: self.quant[1:2])
+    weight_scale = property(lambda self: self.quant[2:3])
+    weight_zp_neg = property(lambda self: self.quant[3:4])
+
+    def _refresh(self, x: torch.Tensor, w: torch.Tensor, fused: bool = False) -> None:
         if not self.training:
+            return
+        if fused:
+            # the two range reductions, then ONE launch for both observers and the four quantisation parameters
+            a_lo, a_hi = torch.aminmax(x.detach())
+            w_lo, w_hi = torch.aminmax(w.detach())
+            approx_ops.layer_update_ranges(a_lo, a_hi, w_lo, w_hi, self.act_range.state(), self.weight_range.state(),
+                                           self.act_range.momentum, self.a_qmax, self.w_qmax, self.quant)
             return
         eps = torch.finfo(torch.float32).eps
         with torch.no_grad():
@@ -278,11 +289,13 @@ class AppConv2d(nn.Conv2d, _AppQuant):
         return self_ops.approx_conv2d_op(xq, wq, **kw)
 
     def forward(self, x):
-        self._refresh(x, self.weight)
         if self.conv_impl == "layer" and not self.use_ste_gradient and x.is_cuda:
-            quant = torch.cat([self.activation_scale, self.activation_zp_neg, self.weight_scale, self.weight_zp_neg])
-            return _AppConvLayer.apply(x, self.weight, self.bias, quant, self.a_qmax, self.w_qmax, self.stride[0],
-                                       self.padding[0], self.dilation[0])
+            self._refresh(x, self.weight, fused=True)
+            # (a copy: the layer's buffer is overwritten by the next step's refresh before this step's backward is
+            # necessarily done with it only when forward passes are stacked; four floats)
+            return _AppConvLayer.apply(x, self.weight, self.bias, self.quant.clone(), self.a_qmax, self.w_qmax,
+                                       self.stride[0], self.padding[0], self.dilation[0])
+        self._refresh(x, self.weight)
         xq = self._codes(x, self.activation_scale, self.activation_zp_neg, self.a_qmax)
         wq = self._codes(self.weight, self.weight_scale, self.weight_zp_neg, self.w_qmax)
         geo = dict(stride=self.stride, padding=self.padding, dilation=self.dilation)
@@ -310,13 +323,13 @@ class AppLinear(nn.Linear, _AppQuant):
         self.impl = impl  # "ops": PyTorch quantisation around the LUT-GEMM op; "layer": the whole-layer kernels
 
     def forward(self, x):
-        self._refresh(x, self.weight)
         lead = x.shape[:-1]
         x2 = x.reshape(-1, self.in_features)
         if self.impl == "layer" and not self.use_ste_gradient and x.is_cuda:
-            quant = torch.cat([self.activation_scale, self.activation_zp_neg, self.weight_scale, self.weight_zp_neg])
-            out = _AppLinearLayer.apply(x2, self.weight, self.bias, quant, self.a_qmax, self.w_qmax)
+            self._refresh(x, self.weight, fused=True)
+            out = _AppLinearLayer.apply(x2, self.weight, self.bias, self.quant.clone(), self.a_qmax, self.w_qmax)
             return out.reshape(*lead, self.out_features)
+        self._refresh(x, self.weight)
         xq = self._codes(x2, self.activation_scale, self.activation_zp_neg, self.a_qmax)
         wq = self._codes(self.weight, self.weight_scale, self.weight_zp_neg, self.w_qmax)
         gemm = self_ops.approx_gemm_baseline_op if self.use_ste_gradient else self_ops.approx_gemm_op

@@ -56,12 +56,20 @@ unsigned long long lutgemm_kernel_launches(void);
 int lutgemm_set_kernel_choice(int forward, int backward, int grad_tile);
 
 /*
- * How the 16 warps of a slab-kernel CTA pass slab buffers to each other, process-wide: 1 (default) = through
- * per-buffer shared-memory barriers with one arrival per warp, so warps may drift by half a read phase;
- * 0 = one CTA-wide barrier per k.  Same results either way; exists for A/B timing and tests.
+ * How the 16 warps of a CTA of the tall gradient slab kernels pass slab buffers to each other, process-wide:
+ * 1 (default) = through per-buffer shared-memory barriers with one arrival per warp, so warps may drift by half a
+ * read phase; 0 = one CTA-wide barrier per k.  Same results either way; exists for A/B timing and tests.
  * No counterpart in the reference.
  */
 int lutgemm_set_handover(int on);
+
+/*
+ * How the forward slab kernel fetches its operand-code chunks when it has the transposed copy of the activation
+ * codes, process-wide: 1 (default) = tiled bulk-tensor copies (TMA) issued by one thread straight into shared
+ * memory, 0 = 16-byte vector loads through registers.  Same results either way; exists for A/B timing and tests.
+ * No counterpart in the reference (its kernels load byte-wise or with 4-byte loads, approx_gemm_forward.cu:142-176).
+ */
+int lutgemm_set_tma(int on);
 
 /* Human-readable text for a status code; for LUTGEMM_E_CUDA the CUDA error behind the calling thread's
  * last such status is appended.  The returned pointer is valid until the thread's next call. */
@@ -264,6 +272,44 @@ int lutgemm_forward_layer(const uint8_t *a, const uint8_t *w, const uint16_t *lu
                           const float *box, const float *sumw_t, const float *taps, const float *s_a, const float *s_w,
                           const float *z_a, const float *z_w, const float *bias, float *out, void *scratch,
                           size_t scratch_bytes, void *stream);
+
+/*
+ * Small one-pass kernels of the layer wiring; each stands for a chain of PyTorch elementwise / slicing kernels of
+ * ApproxConv2d.forward, its observers and their autograd backward (micronet+/app_layers.py:21-53, 147-184).
+ * quant is a device array {s_a, z_a, s_w, z_w} (activation scale, activation zero point, weight scale, weight zero
+ * point, the zero points being round(min / scale)); strides are in elements; nothing synchronises with the host.
+ *
+ * lutgemm_layer_update_ranges: the layer's observers and quantisation parameters in one launch.  act_lo/act_hi,
+ *   w_lo/w_hi: min and max of this batch's activations and of the weights (device scalars); the act_ and w_ state: the
+ *   exponential moving average (keep = 1 - momentum) of the activation range, the running range of the weights and
+ *   their "seen" flags (0 before the first batch), updated in place; quant = {max((amax-amin)/a_qmax, eps),
+ *   round(amin/s_a), max((wmax-wmin)/w_qmax, eps), round(wmin/s_w)}.   (:21-53, :155-160)
+ * lutgemm_layer_weight_prep: wmat[(c*kh+i)*kw+j, co] = uint8(clamp(round(weight[co,c,i,j]/s_w - z_w), 0, qmax)) and
+ *   wsum[co, i*kw+j] = sum_c of those codes.   (:147-150, :173 and the uint8 cast / transposition of
+ *   self_ops/ops_py/approx_ops.py:563-564)
+ * lutgemm_layer_cross_terms: sumw_t[l, co] = sum of wsum[co, t] over the taps t inside the image at output
+ *   position l; taps[l] = Cin * their number (the convolutions with a constant image of :179-180).
+ * lutgemm_layer_window_sum: box[b, oh, ow] = sum of img[b, ., .] over the kernel window (zero padding), img the
+ *   channel sums of the activation codes (the convolution with a constant weight of :178).
+ * lutgemm_layer_window_sum_adjoint: out[b, h, w] = sum of gsum[b, oh, ow] over the windows that contain (h, w).
+ * lutgemm_layer_weight_grad: gw[co,c,i,j] = [0 <= round(weight/s_w - z_w) <= qmax] * s_a *
+ *   (gwmat[(c*kh+i)*kw+j, co] + z_a * tapg[co, i*kw+j]), gw contiguous.
+ */
+int lutgemm_layer_update_ranges(const float *act_lo, const float *act_hi, const float *w_lo, const float *w_hi,
+                                float *act_min, float *act_max, float *act_seen, float *w_min, float *w_max, float *w_seen,
+                                float keep, float momentum, float a_qmax, float w_qmax, float eps, float *quant,
+                                void *stream);
+int lutgemm_layer_weight_prep(const float *weight, long s_co, long s_c, long s_h, long s_w, int Cout, int Cin, int kh, int kw,
+                              const float *quant, float qmax, uint8_t *wmat, float *wsum, void *stream);
+int lutgemm_layer_cross_terms(const float *wsum, int Cout, int Cin, int H, int W, int kh, int kw, int stride, int pad,
+                              int dil, float *sumw_t, float *taps, void *stream);
+int lutgemm_layer_window_sum(const float *img, int B, int H, int W, int kh, int kw, int stride, int pad, int dil,
+                             float *box, void *stream);
+int lutgemm_layer_window_sum_adjoint(const float *gsum, int B, int H, int W, int kh, int kw, int stride, int pad, int dil,
+                                     float *out, void *stream);
+int lutgemm_layer_weight_grad(const float *gwmat, const float *tapg, const float *weight, long s_co, long s_c, long s_h,
+                              long s_w, int Cout, int Cin, int kh, int kw, const float *quant, float qmax, float *gw,
+                              void *stream);
 
 /*
  * Weight gradient only, with no device memory taken from anyone: same result as lutgemm_backward with
