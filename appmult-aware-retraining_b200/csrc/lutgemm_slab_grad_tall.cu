@@ -257,16 +257,26 @@ __global__ void __launch_bounds__(512, 1) slab_grad_tall_kernel(const Args p) {
         const uint32_t y0 = cw & 0xffu, y1 = cw >> 8;
         const uint32_t ub = u_addr + buf * C::U_BYTES + wp * 8;
         if constexpr (C::F32_TABLE) {
+            // all table reads of the warp are issued before the first store, so that they do not wait for each
+            // other's round trip (3 % faster at 7 bits)
+            constexpr int NJ = (Q + 31) / 32;
+            uint32_t r0[NJ], r1[NJ];
 #pragma unroll
-            for (int j = 0; j < (Q + 31) / 32; ++j) {
+            for (int j = 0; j < NJ; ++j) {
                 const int x = lane + 32 * j;
                 if (Q >= 32 || x < Q) {
-                    const uint32_t r0 = lds_u32(tt_addr + (y0 * TTS + x) * 4);
-                    const uint32_t r1 = lds_u32(tt_addr + (y1 * TTS + x) * 4);
-                    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(ub + x * (US * 4)), "r"(r0), "r"(r1) : "memory");
+                    r0[j] = lds_u32(tt_addr + (y0 * TTS + x) * 4);
+                    r1[j] = lds_u32(tt_addr + (y1 * TTS + x) * 4);
                 }
             }
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) {
+                const int x = lane + 32 * j;
+                if (Q >= 32 || x < Q)
+                    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(ub + x * (US * 4)), "r"(r0[j]), "r"(r1[j]) : "memory");
+            }
         } else {
+            // (read - convert - store one j at a time: at 8 bits batching the reads measured slower)
 #pragma unroll
             for (int j = 0; j < HALF / 32; ++j) {
                 const int i = lane + 32 * j;
