@@ -469,6 +469,7 @@ def run_ours(args, rank, world, local_rank):
     dom = int(np.argmax(kern_ms))
     dom_rate = M * K * N / (kern_ms[dom] * 1e-3)
     alg_bytes = [M * K + K * N + 4 * M * N, 4 * M * N + M * K + K * N + 4 * K * N, 4 * M * N + M * K + K * N + 4 * M * K]
+    traffic, traffic_source = ncu_dram_traffic(names[dom], (bits, S, M))
     roofline = {
         "bound": "smem_lsu", "kernel": names[dom], "achieved": dom_rate / 1e9, "peak": peak_lookups / 1e9,
         "unit": "G lookups/s", "frac": dom_rate / peak_lookups,
@@ -479,10 +480,9 @@ def run_ours(args, rank, world, local_rank):
         "hbm": {"achieved_gbs": alg_bytes[dom] / (kern_ms[dom] * 1e-3) / 1e9, "peak_gbs": peaks["hbm_gbs"],
                 "frac": alg_bytes[dom] / (kern_ms[dom] * 1e-3) / 1e9 / peaks["hbm_gbs"], "of": peaks_kind},
         # dram__bytes_read.sum + dram__bytes_write.sum per launch of that kernel: a property of the kernel and the
-        # problem size taken from a separate ncu capture (a profiler cannot run inside a timed run), so it is given
-        # only for the one configuration that was captured, with the capture named
-        "traffic": NCU_DRAM_TRAFFIC["bytes_per_launch"].get(names[dom]) if (bits, S, M) == NCU_DRAM_TRAFFIC["config"] else None,
-        "traffic_source": NCU_DRAM_TRAFFIC["source"] if (bits, S, M) == NCU_DRAM_TRAFFIC["config"] else None,
+        # problem size, read from the committed summary of a separate ncu capture (a profiler cannot run inside a
+        # timed run); null for configurations that were not captured
+        "traffic": traffic, "traffic_source": traffic_source,
         "algorithmic_bytes": alg_bytes[dom],
     }
     ref_cuda = None
@@ -686,12 +686,30 @@ def run_layers(args, local_rank):
             "roofline_peak": roof / 1e9, "roofline_unit": "G lookups/s", "peak_of": peaks_kind}
 
 
-# DRAM traffic of the three main kernels from the ncu capture summarised under profiles/ (bytes per launch)
-NCU_DRAM_TRAFFIC = {
-    "config": (8, 4096, 4096),
-    "bytes_per_launch": {"forward": 118.0e6, "grad_w": 360.8e6, "grad_a": 358.3e6},
-    "source": "ncu --set full capture of one launch per kernel, 8-bit 4096^3 (profiles/slab_kernels_b8_4096.md)",
-}
+# DRAM traffic of the three main kernels: read at run time from the committed summary of the ncu capture of this
+# workload (a profiler cannot run inside a timed run, so the figure is a property of the kernel at that size)
+NCU_TRAFFIC_PROFILE = {"config": (8, 4096, 4096), "file": os.path.join("profiles", "slab_kernels_b8_4096.md")}
+
+
+def ncu_dram_traffic(kernel, config):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of `kernel` ("forward" | "grad_w" | "grad_a") from the
+    metric table of the committed ncu summary, or (None, None) for a workload that was not captured."""
+    if config != NCU_TRAFFIC_PROFILE["config"]:
+        return None, None
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), NCU_TRAFFIC_PROFILE["file"])
+    try:
+        rows = [[c.strip() for c in line.strip().strip("|").split("|")] for line in open(path) if line.startswith("|")]
+        header = next(r for r in rows if r and r[0] == "metric")
+        col = next(i for i, c in enumerate(header) if f"({kernel})" in c)
+        scale = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}
+        total = 0.0
+        for name in ("dram__bytes_read.sum", "dram__bytes_write.sum"):
+            r = next(r for r in rows if r[0] == name)
+            total += float(r[col].replace(",", "")) * scale[r[1]]
+        return total, f"ncu --set full capture of one launch of this kernel at this size ({NCU_TRAFFIC_PROFILE['file']})"
+    except (OSError, StopIteration, ValueError, KeyError, IndexError):
+        return None, None
+
 
 WORKLOAD_NAMES = {"resnet18": "ResNet-18 CIFAR-shape", "resnet50": "ResNet-50 ImageNet-shape", "vit_s": "ViT-S/16"}
 # per-workload defaults of the benchmark configurations: (bits, per-GPU batch)

@@ -76,3 +76,17 @@ def test_conv_op_rejects_bias_and_groups():
         self_ops.approx_conv2d_op(x, w, bias=torch.zeros(3), stride=(1, 1), padding=(1, 1), dilation=(1, 1), groups=1)
     with pytest.raises(AssertionError):
         self_ops.approx_conv2d_op(x, w, bias=None, stride=(1, 1), padding=(1, 1), dilation=(1, 1), groups=2)
+
+
+def test_bench_reads_dram_traffic_from_the_committed_capture_summary():
+    """bench.py's roofline.traffic is parsed from the ncu summary under profiles/, only for the captured workload."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import bench
+    for kernel in ("forward", "grad_w", "grad_a"):
+        nbytes, source = bench.ncu_dram_traffic(kernel, (8, 4096, 4096))
+        assert nbytes is not None and 50e6 < nbytes < 2e9, kernel
+        assert "profiles/" in source
+    assert bench.ncu_dram_traffic("forward", (7, 4096, 4096)) == (None, None)
+    assert bench.ncu_dram_traffic("no such kernel", (8, 4096, 4096)) == (None, None)
