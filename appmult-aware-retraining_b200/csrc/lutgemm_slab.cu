@@ -15,8 +15,10 @@
 // codes x and x + 2^b/2 in one word) with conflict-free 32-bit loads and writes slab rows (stride 34
 // words) with conflict-free 64-bit stores: 2^b * 2 wavefronts per k against 512 for the use phase.
 // Two slab buffers: slab k+1 is built while slab k is read, one CTA barrier per k.  (Handing the buffers over
-// through per-buffer mbarriers, as the gradient kernels do, was measured SLOWER here - 11.5 against 10.7 ms at
-// 8 bits, 9.7 against 8.9 ms at 7 bits for 4096^3 - the forward's read phase per k is half as long as theirs.)
+// through per-buffer mbarriers, as the gradient kernels do, does not pay here: with polling waits it was slower -
+// 11.5 against 10.7 ms at 8 bits for 4096^3 - and with suspending waits 10.38 against 10.42 ms at 8 bits, 8.63
+// against 8.68 ms at 7 bits, 8.35 against 7.69 ms at 6 bits: the forward's read phase per k is half as long as
+// the gradients'.)
 // The two halves of a slab word go to the accumulators as  S += word,  H += word >> 16 ; at the end
 // sum(lo) = S - (H << 16) (mod 2^32) and sum(hi) = H.
 // Work items are (tile, K split); splits of one tile are combined with integer atomics, which are

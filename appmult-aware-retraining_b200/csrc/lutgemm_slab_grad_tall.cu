@@ -256,40 +256,45 @@ __global__ void __launch_bounds__(512, 1) slab_grad_tall_kernel(const Args p) {
         const uint32_t cw = *reinterpret_cast<const uint16_t *>(cc_s + stage * C::CC_STAGE + kk * CT + wp * 2);
         const uint32_t y0 = cw & 0xffu, y1 = cw >> 8;
         const uint32_t ub = u_addr + buf * C::U_BYTES + wp * 8;
-        if constexpr (C::F32_TABLE) {
-            // all table reads of the warp are issued before the first store, so that they do not wait for each
-            // other's round trip (3 % faster at 7 bits)
-            constexpr int NJ = (Q + 31) / 32;
-            uint32_t r0[NJ], r1[NJ];
-#pragma unroll
-            for (int j = 0; j < NJ; ++j) {
-                const int x = lane + 32 * j;
-                if (Q >= 32 || x < Q) {
-                    r0[j] = lds_u32(tt_addr + (y0 * TTS + x) * 4);
-                    r1[j] = lds_u32(tt_addr + (y1 * TTS + x) * 4);
-                }
+        // The table reads of the warp's share are issued before its first store where that measured faster (the
+        // stores order later reads behind them): always with the fp32 table (7 bits: grad_w 13.70 -> 13.28 ms,
+        // grad_a 13.87 -> 13.48 ms at 4096^3), at 8 bits for grad_w only (14.00 -> 13.77 ms; grad_a 14.06 -> 14.50 ms).
+        constexpr bool READS_FIRST = C::F32_TABLE || MODE == kGw;
+        constexpr int NJ = C::F32_TABLE ? (Q + 31) / 32 : HALF / 32;
+        uint32_t r0[NJ], r1[NJ];
+        auto read = [&](int j) {
+            const int x = lane + 32 * j;  // fp32 table: code x; int16 table: the pair of codes (x, x + HALF)
+            if (Q >= 32 || x < Q) {
+                r0[j] = lds_u32(tt_addr + (y0 * TTS + x) * 4);
+                r1[j] = lds_u32(tt_addr + (y1 * TTS + x) * 4);
             }
-#pragma unroll
-            for (int j = 0; j < NJ; ++j) {
-                const int x = lane + 32 * j;
+        };
+        auto store = [&](int j) {
+            const int x = lane + 32 * j;
+            if constexpr (C::F32_TABLE) {
                 if (Q >= 32 || x < Q)
                     asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(ub + x * (US * 4)), "r"(r0[j]), "r"(r1[j]) : "memory");
-            }
-        } else {
-            // (read - convert - store one j at a time: at 8 bits batching the reads measured slower)
-#pragma unroll
-            for (int j = 0; j < HALF / 32; ++j) {
-                const int i = lane + 32 * j;
-                const uint32_t r0 = lds_u32(tt_addr + (y0 * TTS + i) * 4);
-                const uint32_t r1 = lds_u32(tt_addr + (y1 * TTS + i) * 4);
+            } else {
                 // 0x4B000000 | u is the float 2^23 + u; minus (2^23 + 32768) leaves the signed entry exactly
-                const float f00 = __uint_as_float((r0 & 0xffffu) | 0x4B000000u) - 8421376.0f;
-                const float f01 = __uint_as_float((r1 & 0xffffu) | 0x4B000000u) - 8421376.0f;
-                const float f10 = __uint_as_float(__byte_perm(r0, 0x4B000000u, 0x7632)) - 8421376.0f;
-                const float f11 = __uint_as_float(__byte_perm(r1, 0x4B000000u, 0x7632)) - 8421376.0f;
-                asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(ub + i * (US * 4)), "f"(f00), "f"(f01) : "memory");
-                asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(ub + (i + HALF) * (US * 4)), "f"(f10), "f"(f11)
+                const float f00 = __uint_as_float((r0[j] & 0xffffu) | 0x4B000000u) - 8421376.0f;
+                const float f01 = __uint_as_float((r1[j] & 0xffffu) | 0x4B000000u) - 8421376.0f;
+                const float f10 = __uint_as_float(__byte_perm(r0[j], 0x4B000000u, 0x7632)) - 8421376.0f;
+                const float f11 = __uint_as_float(__byte_perm(r1[j], 0x4B000000u, 0x7632)) - 8421376.0f;
+                asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(ub + x * (US * 4)), "f"(f00), "f"(f01) : "memory");
+                asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(ub + (x + HALF) * (US * 4)), "f"(f10), "f"(f11)
                              : "memory");
+            }
+        };
+        if constexpr (READS_FIRST) {
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) read(j);
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) store(j);
+        } else {
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) {
+                read(j);
+                store(j);
             }
         }
     };
