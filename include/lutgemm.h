@@ -346,7 +346,7 @@ int lutgemm_device_error(int *value);
 
 /*
  * Launches a one-warp kernel that waits on a shared-memory barrier nothing ever arrives on.  The wait
- * is bounded like every wait in the library: it gives up after a fraction of a second, records error
+ * is bounded like every wait in the library: it gives up after one second, records error
  * id 99 (readable through lutgemm_device_error) and the kernel returns; the context stays usable.
  * Exists so that the time-out path can be exercised without hanging a GPU.  No counterpart in the
  * reference.
