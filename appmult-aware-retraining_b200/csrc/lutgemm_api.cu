@@ -412,13 +412,21 @@ static bool pixel_mode_supported(const lutgemm::ConvGeom &g) {
 }
 
 // Per stride class: the slab kernel in pixel mode pays where its row dimension taps * Cout is long enough to
-// amortise the slab build (measured on B200: from about 4096 rows at 7 and 8 bits); otherwise, and always at 4 and
-// 6 bits where a table row is free of bank conflicts, the column-broadcast gather kernel in pixel mode.
+// amortise the slab build; otherwise, and always at 4 and 6 bits where a table row is free of bank conflicts, the
+// column-broadcast gather kernel in pixel mode.  The slab kernel's time does not depend on the codes; the broadcast
+// kernel's bank conflicts do (weight codes clustered around the zero point conflict less than uniform ones).
+// Measured on B200, ResNet-18 layers at batch 256, broadcast with uniform / clustered codes against slab, ms:
+//   7 bits  3x3 512->512 (4608 rows) 2.92 / 2.13 : 2.42    3x3 256->256 (2304 rows) 2.91 / 2.12 : 3.13
+//   8 bits  3x3 512->512             3.94 / 2.73 : 2.68    3x3 256->256             3.92 / 2.69 : 3.63
+//           3x3 256->512 stride 2 (classes of 2048, 1024, 1024, 512 rows) 2.63 / 1.82 : 1.53
+// Trained layers have clustered codes, so the choice leans that way: from 8192 rows at 7 bits (a wash between the two
+// distributions at 4608), from 4096 rows or Cout >= 512 at 8 bits, where the gather is up to four-way conflicted.
 static bool gx_class_uses_slab(int bits, const lutgemm::PixelClass &px, int Cout) {
     const int force = g_force_backward.load(std::memory_order_relaxed);
     if (force == LUTGEMM_BACKWARD_BCAST) return false;
     if (force == LUTGEMM_BACKWARD_SLAB) return true;
-    return bits >= 7 && (long)px.ntaps * Cout >= 4096;
+    const long rows = (long)px.ntaps * Cout;
+    return bits == 7 ? rows >= 8192 : bits == 8 && (rows >= 4096 || Cout >= 512);
 }
 
 static size_t conv_gx_scratch_bytes(int bits, const lutgemm::ConvGeom &g, int Cout) {

@@ -637,7 +637,8 @@ def run_layers(args, local_rank):
     """--workload resnet18_layers: every distinct convolution of the network on its own - forward, grad_w and
     grad_x in ms (CUDA events) and as a fraction of the look-up roofline, plus per-step totals weighted by how
     often the layer occurs.  Each call is timed alone, so grad_w includes the code transposition that a
-    training step shares with the forward pass."""
+    training step shares with the forward pass.  The slab kernels' times do not depend on the codes, the broadcast
+    kernels' bank conflicts do: --codes clustered draws them as a trained layer has them."""
     import torch
 
     import approx_ops
@@ -665,8 +666,16 @@ def run_layers(args, local_rank):
 
     rows, tot = [], [0.0, 0.0, 0.0]
     for name, cin, hw, cout, k, st, p, cnt in RESNET18_LAYERS:
-        x = torch.randint(0, 1 << bits, (B, cin, hw, hw), dtype=torch.uint8, device=dev)
-        wm = torch.randint(0, 1 << bits, (cin * k * k, cout), dtype=torch.uint8, device=dev)
+        if args.codes == "clustered":
+            # codes as a trained layer has them: weights normal around the zero point, activations after a ReLU
+            q = 1 << bits
+            w = torch.randn(cin * k * k, cout, device=dev)
+            wm = (torch.round(w / (w.abs().max() / (q / 2 - 1))) + q / 2).clamp(0, q - 1).to(torch.uint8)
+            xa = torch.relu(torch.randn(B, cin, hw, hw, device=dev))
+            x = torch.round(xa / (xa.max() / (q - 1))).clamp(0, q - 1).to(torch.uint8)
+        else:
+            x = torch.randint(0, 1 << bits, (B, cin, hw, hw), dtype=torch.uint8, device=dev)
+            wm = torch.randint(0, 1 << bits, (cin * k * k, cout), dtype=torch.uint8, device=dev)
         ho = (hw + 2 * p - k) // st + 1
         M, K = B * ho * ho, cin * k * k
         y = torch.empty(M, cout, dtype=torch.uint32, device=dev)
@@ -681,7 +690,7 @@ def run_layers(args, local_rank):
                      "grad_w_ms": tw, "grad_w_frac": frac(tw), "grad_x_ms": tx, "grad_x_frac": frac(tx)})
         for i, t in enumerate((tf, tw, tx)):
             tot[i] += t * cnt
-    return {"metric": "appmult_resnet18_layer_times", "unit": "ms", "bits": bits, "batch": B, "layers": rows,
+    return {"metric": "appmult_resnet18_layer_times", "unit": "ms", "bits": bits, "batch": B, "codes": args.codes, "layers": rows,
             "per_step_ms": {"forward": tot[0], "grad_w": tot[1], "grad_x": tot[2], "sum": sum(tot)},
             "roofline_peak": roof / 1e9, "roofline_unit": "G lookups/s", "peak_of": peaks_kind}
 
@@ -731,6 +740,8 @@ def main():
     ap.add_argument("--shard-m", action="store_true",
                     help="lutgemm workload: cut the M rows of ONE size^3 problem across the ranks (strong scaling)")
     ap.add_argument("--ste", action="store_true", help="model workloads: straight-through backward instead of the gradient tables")
+    ap.add_argument("--codes", choices=["uniform", "clustered"], default="uniform",
+                    help="resnet18_layers: uniform random codes, or codes distributed like a trained layer's")
     ap.add_argument("--no-parity-gate", action="store_true", help="lutgemm workload: skip the sampled oracle comparison")
     ap.add_argument("--no-reference-cuda", action="store_true",
                     help="lutgemm workload: do not time the reference's own CUDA kernels beside ours")
