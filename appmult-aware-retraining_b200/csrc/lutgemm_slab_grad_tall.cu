@@ -35,6 +35,10 @@
 #include "lutgemm_kernels.h"
 #include "lutgemm_waits.cuh"
 
+#ifndef LUTGEMM_TALL_HALFWARP_ROWS
+#define LUTGEMM_TALL_HALFWARP_ROWS 1
+#endif
+
 namespace lutgemm {
 namespace sgt {
 
@@ -99,6 +103,9 @@ __global__ void __launch_bounds__(512, 1) slab_grad_tall_kernel(const Args p) {
     constexpr int US = C::U_STRIDE, PS = C::P_STRIDE, THREADS = C::THREADS, NSEG = C::NSEG, RCL = C::RC_LOADS;
     constexpr int HALVES = KC / SC;  // shared-memory stages per fetched group of 16 k
     constexpr int PF = 4;            // slab reads in flight ahead of their use (2 to 16 measured alike)
+    // HW: half a warp per slab row and two columns per lane (64-bit slab reads) instead of a warp per row and one
+    // column per lane: lanes 0-15 take the first RW/2 rows of the warp, lanes 16-31 the others
+    constexpr bool HW = LUTGEMM_TALL_HALFWARP_ROWS && MODE != kGx && RW == 64 && HANDOVER;
     constexpr uint32_t MASK4 = (Q - 1) * 0x01010101u;
     constexpr int COL = lut_col_num(BITS);
     static_assert(MODE != kGw || USE_AT || RT % THREADS == 0, "grad_w without a transposed copy: whole rows per thread");
@@ -331,7 +338,42 @@ __global__ void __launch_bounds__(512, 1) slab_grad_tall_kernel(const Args p) {
 
         // the grad_out block of this tile: g[r] for the warp's RW rows and the lane's column
         float g[RW];
-        if (MODE == kGw) {
+        if constexpr (HW) {
+            // g[2i + j] = grad_out at (row h * RW/2 + i of the warp, column 2 * cp + j of the tile)
+            const int h = lane >> 4, cp = lane & 15;
+            if (MODE == kGw) {
+                const int n = c0 + 2 * cp;
+#pragma unroll
+                for (int i = 0; i < RW / 2; ++i) {
+                    const int m = r0 + wp * RW + h * (RW / 2) + i;
+                    if (m < M && n + 1 < N && p.vec_g) {
+                        const float2 t = *reinterpret_cast<const float2 *>(p.gc + (size_t)m * N + n);
+                        g[2 * i] = t.x; g[2 * i + 1] = t.y;
+                    } else {
+                        g[2 * i] = (m < M && n < N) ? p.gc[(size_t)m * N + n] : 0.f;
+                        g[2 * i + 1] = (m < M && n + 1 < N) ? p.gc[(size_t)m * N + n + 1] : 0.f;
+                    }
+                }
+            } else {
+                const int nb = r0 + wp * RW + h * (RW / 2);
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int m = c0 + 2 * cp + j;
+                    const float *src = p.gc + (size_t)min(m, M - 1) * N + min(nb, N - 1);
+                    if (m < M && p.vec_g && nb + RW / 2 <= N) {
+#pragma unroll
+                        for (int i = 0; i < RW / 2; i += 4) {
+                            const float4 t = *reinterpret_cast<const float4 *>(src + i);
+                            g[2 * i + j] = t.x; g[2 * (i + 1) + j] = t.y; g[2 * (i + 2) + j] = t.z; g[2 * (i + 3) + j] = t.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < RW / 2; ++i)
+                            g[2 * i + j] = (m < M && nb + i < N) ? p.gc[(size_t)m * N + nb + i] : 0.f;
+                    }
+                }
+            }
+        } else if (MODE == kGw) {
             const int n = c0 + lane;
 #pragma unroll
             for (int r = 0; r < RW; ++r) {
@@ -452,9 +494,39 @@ __global__ void __launch_bounds__(512, 1) slab_grad_tall_kernel(const Args p) {
                 s[r & 3] = fmaf(f, g[r], s[r & 3]);
             }
         };
+        // HW: rows [IB, IE) of this half-warp's RW/2 rows; s[0], s[2] belong to the lane's first column, s[1], s[3] to
+        // its second
+        auto use_rows_hw = [&](int k, int stage, int kk, float (&s)[4], auto ib_tag, auto ie_tag) {
+            constexpr int IB = decltype(ib_tag)::value, IEND = decltype(ie_tag)::value;
+            static_assert(IB % 16 == 0 && IEND % 16 == 0, "whole 16-row code vectors");
+            const uint8_t *rbase = rc_s + stage * C::RC_STAGE + kk * RT + wp * RW + (lane >> 4) * (RW / 2);
+            const uint32_t ub = u_addr + (k & 1) * C::U_BYTES + (lane & 15) * 8;
+            uint32_t rv[(IEND - IB) / 4];
+#pragma unroll
+            for (int q = IB / 16; q < IEND / 16; ++q) {
+                const uint4 t = reinterpret_cast<const uint4 *>(rbase)[q];
+                rv[4 * q - IB / 4] = t.x; rv[4 * q + 1 - IB / 4] = t.y; rv[4 * q + 2 - IB / 4] = t.z; rv[4 * q + 3 - IB / 4] = t.w;
+            }
+            float pa[PF], pb[PF];
+            auto fetch = [&](int i) {
+                asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];"
+                             : "=f"(pa[(i - IB) % PF]), "=f"(pb[(i - IB) % PF])
+                             : "r"(byte_scaled_add<US * 4>(rv[(i - IB) >> 2], i & 3, ub)));
+            };
+#pragma unroll
+            for (int i = IB; i < IB + PF; ++i) fetch(i);
+#pragma unroll
+            for (int i = IB; i < IEND; ++i) {
+                const float fa = pa[(i - IB) % PF], fb = pb[(i - IB) % PF];
+                if (i + PF < IEND) fetch(i + PF);
+                s[2 * (i & 1)] = fmaf(fa, g[2 * i], s[2 * (i & 1)]);
+                s[2 * (i & 1) + 1] = fmaf(fb, g[2 * i + 1], s[2 * (i & 1) + 1]);
+            }
+        };
         using I0 = std::integral_constant<int, 0>;
         using IH = std::integral_constant<int, (RW / 2) & ~3>;
         using IE = std::integral_constant<int, RW>;
+        using IQ = std::integral_constant<int, ((RW / 4) + 15) & ~15>;  // HW: half of a half-warp's rows
 
         for (int k = kbeg; k < kend; ++k) {
             const int chunk = k / SC, kk = k % SC, stage = chunk & 1;
@@ -467,7 +539,8 @@ __global__ void __launch_bounds__(512, 1) slab_grad_tall_kernel(const Args p) {
                 const int b = k & 1;
                 const uint32_t par = ((k - kbeg) >> 1) & 1;
                 mbar_wait(bar_full + 8 * b, par, 1 + b, abort_word, p.error_word);         // slab k is complete
-                use_rows(k, stage, kk, s, I0{}, IH{});
+                if constexpr (HW) use_rows_hw(k, stage, kk, s, I0{}, IQ{});
+                else use_rows(k, stage, kk, s, I0{}, IH{});
                 mbar_wait(bar_empty + 8 * (b ^ 1), par, 3 + b, abort_word, p.error_word);  // slab k-1 is released
                 if (k > kbeg && wp == ((k - 1) & (WARPS - 1))) reduce_store(k - 1, obase, c0);
                 if (k + 1 < kend) {
@@ -476,8 +549,21 @@ __global__ void __launch_bounds__(512, 1) slab_grad_tall_kernel(const Args p) {
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_full + 8 * (b ^ 1));
                 }
-                use_rows(k, stage, kk, s, IH{}, IE{});
-                part_s[(k & 1) * (WARPS * PS) + wp * PS + lane] = (s[0] + s[1]) + (s[2] + s[3]);
+                if constexpr (HW) {
+                    use_rows_hw(k, stage, kk, s, IQ{}, IH{});
+                    // the two halves of the warp hold the same two columns for different rows
+                    float ca = s[0] + s[2], cb = s[1] + s[3];
+                    ca += __shfl_xor_sync(0xffffffffu, ca, 16);
+                    cb += __shfl_xor_sync(0xffffffffu, cb, 16);
+                    if (lane < 16) {
+                        float *pp = part_s + (k & 1) * (WARPS * PS) + wp * PS + 2 * lane;
+                        pp[0] = ca;
+                        pp[1] = cb;
+                    }
+                } else {
+                    use_rows(k, stage, kk, s, IH{}, IE{});
+                    part_s[(k & 1) * (WARPS * PS) + wp * PS + lane] = (s[0] + s[1]) + (s[2] + s[3]);
+                }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_empty + 8 * b);
             } else {
