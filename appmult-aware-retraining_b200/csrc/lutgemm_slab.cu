@@ -40,6 +40,10 @@
 #include "lutgemm_tma.cuh"
 #include "lutgemm_waits.cuh"
 
+#ifndef LUTGEMM_FWD_HALFWARP_ROWS
+#define LUTGEMM_FWD_HALFWARP_ROWS 1
+#endif
+
 namespace lutgemm {
 namespace sf {
 
@@ -93,6 +97,7 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p, const __
     constexpr int US = C::U_STRIDE, THREADS = C::THREADS, NSETS = C::NSETS;
     constexpr uint32_t MASK4 = (Q - 1) * 0x01010101u;
     constexpr int COL = lut_col_num(BITS);
+    constexpr bool HW = LUTGEMM_FWD_HALFWARP_ROWS != 0;  // half a warp per slab row in the use phase (64-bit reads)
     const int M = p.M, K = p.K, N = p.N;
 
     extern __shared__ __align__(128) uint8_t smem[];
@@ -210,7 +215,9 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p, const __
         const int kbeg = (item % p.ksplits) * p.k_per_split, kend = min(K, kbeg + p.k_per_split);
         const int m0 = (tile / p.tiles_c) * RT, n0 = (tile % p.tiles_c) * CT;
 
-        uint32_t acc[32][2];  // [row][0] = sum of whole words, [row][1] = sum of high halves
+        // HW: half a warp per slab row, two words (four columns) per lane: acc[2 * i + w] belongs to row i of the lane's
+        // half and word w.  Otherwise a warp per row, one word (two columns) per lane: acc[r] belongs to row r.
+        uint32_t acc[32][2];  // [..][0] = sum of whole words, [..][1] = sum of high halves
 #pragma unroll
         for (int r = 0; r < 32; ++r) acc[r][0] = acc[r][1] = 0u;
 
@@ -238,31 +245,52 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p, const __
             } else if (kk == 0 && have_next_chunk) fetch_chunk(m0, n0, chunk + 1);
             if (k + 1 < kend) build((k + 1) & 1, ((k + 1) / KC) & 1, (k + 1) % KC);
 
-            // use slab k: slab row a[m,k], two columns per lane, for this warp's 32 rows
-            const uint4 *rp = reinterpret_cast<const uint4 *>(rc_s + stage * C::RC_STAGE + rc_off(kk, wp * 32));
-            const uint4 q0 = rp[0], q1 = rp[1];
-            const uint32_t rv[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-            const uint32_t ub = u_addr + (k & 1) * C::U_BYTES + lane * 4;
+            if constexpr (HW) {
+                // use slab k: lanes 0-15 read the slab rows of the warp's rows 0-15, lanes 16-31 those of rows 16-31,
+                // 64 bits (four columns) per lane
+                const uint4 q0 = *reinterpret_cast<const uint4 *>(rc_s + stage * C::RC_STAGE +
+                                                                  rc_off(kk, wp * 32 + (lane >> 4) * 16));
+                const uint32_t rv[4] = {q0.x, q0.y, q0.z, q0.w};
+                const uint32_t ub = u_addr + (k & 1) * C::U_BYTES + (lane & 15) * 8;
 #pragma unroll
-            for (int r = 0; r < 32; ++r) {
-                // slab row address = base + 136 * code in one integer dot-product instruction
-                const uint32_t addr = byte_scaled_add<US * 4>(rv[r >> 2], r & 3, ub);
-                uint32_t word;
-                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(word) : "r"(addr));
-                acc[r][0] += word;
-                acc[r][1] += word >> 16;
+                for (int i = 0; i < 16; ++i) {
+                    // slab row address = base + 136 * code in one integer dot-product instruction
+                    const uint32_t addr = byte_scaled_add<US * 4>(rv[i >> 2], i & 3, ub);
+                    uint32_t w0, w1;
+                    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(w0), "=r"(w1) : "r"(addr));
+                    acc[2 * i][0] += w0;
+                    acc[2 * i][1] += w0 >> 16;
+                    acc[2 * i + 1][0] += w1;
+                    acc[2 * i + 1][1] += w1 >> 16;
+                }
+            } else {
+                // use slab k: slab row a[m,k], two columns per lane, for this warp's 32 rows
+                const uint4 *rp = reinterpret_cast<const uint4 *>(rc_s + stage * C::RC_STAGE + rc_off(kk, wp * 32));
+                const uint4 q0 = rp[0], q1 = rp[1];
+                const uint32_t rv[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+                const uint32_t ub = u_addr + (k & 1) * C::U_BYTES + lane * 4;
+#pragma unroll
+                for (int r = 0; r < 32; ++r) {
+                    // slab row address = base + 136 * code in one integer dot-product instruction
+                    const uint32_t addr = byte_scaled_add<US * 4>(rv[r >> 2], r & 3, ub);
+                    uint32_t word;
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(word) : "r"(addr));
+                    acc[r][0] += word;
+                    acc[r][1] += word >> 16;
+                }
             }
             if (!TMA && kk == KC - 2 && have_next_chunk) store_chunk(stage ^ 1);
             __syncthreads();
         }
 
-        const int n = n0 + 2 * lane;
         LayerEpilogueScalars ev{};
         if (p.epi.out) ev = load_epilogue_scalars(p.epi);
 #pragma unroll
         for (int r = 0; r < 32; ++r) {
             acc[r][0] -= acc[r][1] << 16;  // low-half sum = whole-word sum - 65536 * high-half sum
-            const int m = m0 + wp * 32 + r;
+            // the row and the first of the two columns that acc[r] holds
+            const int m = HW ? m0 + wp * 32 + (lane >> 4) * 16 + (r >> 1) : m0 + wp * 32 + r;
+            const int n = HW ? n0 + 4 * (lane & 15) + 2 * (r & 1) : n0 + 2 * lane;
             if (m < M) {
                 if (p.epi.out) {
                     // the layer's de-quantisation applied to the sums in registers (one split per tile here)
