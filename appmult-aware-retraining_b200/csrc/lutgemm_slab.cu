@@ -243,7 +243,11 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p, const __
                 if (kk == 0 && have_next_chunk) tma_issue(m0, n0, chunk + 1, stage ^ 1);
                 if (kk == KC - 1 && have_next_chunk) tma_wait(stage ^ 1);
             } else if (kk == 0 && have_next_chunk) fetch_chunk(m0, n0, chunk + 1);
-            if (k + 1 < kend) build((k + 1) & 1, ((k + 1) / KC) & 1, (k + 1) % KC);
+            // half of the warps (alternating groups of four, so that every scheduler has both kinds) build their share
+            // of slab k+1 before their reads of slab k, the other half after them: the build's dependent
+            // shared-memory chains then overlap read streams
+            const bool build_first = (wp >> 2) & 1;
+            if (build_first && k + 1 < kend) build((k + 1) & 1, ((k + 1) / KC) & 1, (k + 1) % KC);
 
             if constexpr (HW) {
                 // use slab k: lanes 0-15 read the slab rows of the warp's rows 0-15, lanes 16-31 those of rows 16-31,
@@ -279,6 +283,7 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p, const __
                     acc[r][1] += word >> 16;
                 }
             }
+            if (!build_first && k + 1 < kend) build((k + 1) & 1, ((k + 1) / KC) & 1, (k + 1) % KC);
             if (!TMA && kk == KC - 2 && have_next_chunk) store_chunk(stage ^ 1);
             __syncthreads();
         }

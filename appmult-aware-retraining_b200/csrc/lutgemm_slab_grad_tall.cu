@@ -102,7 +102,9 @@ __global__ void __launch_bounds__(512, 1) slab_grad_tall_kernel(const Args p) {
     constexpr int Q = C::Q, HALF = C::HALF, TTS = C::TT_STRIDE, RT = C::RT, CT = C::CT, KC = C::KC, SC = C::SC;
     constexpr int US = C::U_STRIDE, PS = C::P_STRIDE, THREADS = C::THREADS, NSEG = C::NSEG, RCL = C::RC_LOADS;
     constexpr int HALVES = KC / SC;  // shared-memory stages per fetched group of 16 k
-    constexpr int PF = 4;            // slab reads in flight ahead of their use (2 to 16 measured alike)
+    // slab reads in flight ahead of their use (per row, or per pair of columns with HW): 4 at 8 bits (2 and 3 are 1 - 2 %
+    // slower, 8 is 3 % slower), 2 at 7 bits and below (4 is 1 % slower)
+    constexpr int PF = BITS == 8 ? 4 : 2;
     // HW: half a warp per slab row and two columns per lane (64-bit slab reads) instead of a warp per row and one
     // column per lane: lanes 0-15 take the first RW/2 rows of the warp, lanes 16-31 the others
     constexpr bool HW = LUTGEMM_TALL_HALFWARP_ROWS && MODE != kGx && RW == 64 && HANDOVER;
