@@ -175,19 +175,28 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p, const __
         // (chunks that arrive by bulk copy have not been through the masking store: cut the codes to BITS bits here)
         const uint32_t cwm = TMA ? (cw & MASK4) : cw;
         const uint32_t y0 = byte_of(cwm, 0), y1 = byte_of(cwm, 1), y2 = byte_of(cwm, 2), y3 = byte_of(cwm, 3);
+        // all table reads of the warp's share are issued before its first store (the stores order later reads behind
+        // them)
+        uint32_t r0[NSETS], r1[NSETS], r2[NSETS], r3[NSETS];
 #pragma unroll
         for (int j = 0; j < NSETS; ++j) {
             const int i = lane + 32 * j;
             if (HALF >= 32 || i < HALF) {
-                const uint32_t r0 = lds_u32(tt_addr + (y0 * TTS + i) * 4);
-                const uint32_t r1 = lds_u32(tt_addr + (y1 * TTS + i) * 4);
-                const uint32_t r2 = lds_u32(tt_addr + (y2 * TTS + i) * 4);
-                const uint32_t r3 = lds_u32(tt_addr + (y3 * TTS + i) * 4);
+                r0[j] = lds_u32(tt_addr + (y0 * TTS + i) * 4);
+                r1[j] = lds_u32(tt_addr + (y1 * TTS + i) * 4);
+                r2[j] = lds_u32(tt_addr + (y2 * TTS + i) * 4);
+                r3[j] = lds_u32(tt_addr + (y3 * TTS + i) * 4);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < NSETS; ++j) {
+            const int i = lane + 32 * j;
+            if (HALF >= 32 || i < HALF) {
                 // { LUT[i][y0], LUT[i][y1] }, { LUT[i][y2], LUT[i][y3] } and the same for code i + HALF
-                asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(ub + i * (US * 4)), "r"(__byte_perm(r0, r1, 0x5410)),
-                             "r"(__byte_perm(r2, r3, 0x5410)) : "memory");
+                asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(ub + i * (US * 4)), "r"(__byte_perm(r0[j], r1[j], 0x5410)),
+                             "r"(__byte_perm(r2[j], r3[j], 0x5410)) : "memory");
                 asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(ub + (i + HALF) * (US * 4)),
-                             "r"(__byte_perm(r0, r1, 0x7632)), "r"(__byte_perm(r2, r3, 0x7632)) : "memory");
+                             "r"(__byte_perm(r0[j], r1[j], 0x7632)), "r"(__byte_perm(r2[j], r3[j], 0x7632)) : "memory");
             }
         }
     };
