@@ -643,6 +643,34 @@ __global__ void __launch_bounds__(256) transpose_codes_plane_kernel(const uint8_
     }
 }
 
+// Plain [M,K] matrix with 16-byte aligned rows (K a multiple of 16): a CTA moves a tile of 128 rows x 64 k through
+// shared memory - 16-byte loads along k, 16-byte stores along m - instead of gathering single bytes from global memory.
+__global__ void __launch_bounds__(512) transpose_codes_tiled_kernel(const uint8_t *__restrict__ a, uint8_t *__restrict__ at,
+                                                                    int M, int K, int pitch, uint32_t mask4) {
+    constexpr int TM = 128, TK = 64, TP = TK + 4;  // tile pitch in bytes: rows 17 words apart, the transposed byte reads
+                                                   // of 32 rows fall on 32 different banks
+    __shared__ __align__(16) uint8_t tile[TM * TP];
+    const int m0 = blockIdx.x * TM, k0 = blockIdx.y * TK;
+    const int tid = threadIdx.x;
+    {   // load: thread = (row, 16-k chunk); 4 chunks per row
+        const int r = tid >> 2, q = tid & 3;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (m0 + r < M && k0 + q * 16 < K) v = *reinterpret_cast<const uint4 *>(a + (size_t)(m0 + r) * K + k0 + q * 16);
+        uint32_t *dst = reinterpret_cast<uint32_t *>(tile + r * TP + q * 16);
+        dst[0] = v.x & mask4; dst[1] = v.y & mask4; dst[2] = v.z & mask4; dst[3] = v.w & mask4;
+    }
+    __syncthreads();
+    {   // store: thread = (k, 16-row chunk); 8 chunks per k
+        const int k = tid >> 3, c = tid & 7;
+        if (k0 + k < K && m0 + c * 16 < pitch) {
+            uint32_t v[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+            for (int e = 0; e < 16; ++e) v[e >> 2] |= (uint32_t)tile[(c * 16 + e) * TP + k] << (8 * (e & 3));
+            *reinterpret_cast<uint4 *>(at + (size_t)(k0 + k) * pitch + m0 + c * 16) = make_uint4(v[0], v[1], v[2], v[3]);
+        }
+    }
+}
+
 int transpose_codes(const uint8_t *a, uint8_t *at, int M, int K, int pitch, const ConvGeom &conv, int bits,
                     cudaStream_t stream) {
     const uint32_t mask4 = ((1u << bits) - 1u) * 0x01010101u;  // codes are cut to `bits` bits on their way through
@@ -655,6 +683,11 @@ int transpose_codes(const uint8_t *a, uint8_t *at, int M, int K, int pitch, cons
             !cuda_ok(cudaFuncSetAttribute(transpose_codes_plane_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)))
             return LUTGEMM_E_CUDA;
         transpose_codes_plane_kernel<<<conv.B * conv.C, 256, smem, stream>>>(a, at, pitch, conv, mask4);
+        return launch_status();
+    }
+    if (!conv.enabled && K % 16 == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0 && (K + 63) / 64 <= 65535) {
+        const dim3 tgrid((pitch + 127) / 128, (K + 63) / 64);
+        transpose_codes_tiled_kernel<<<tgrid, 512, 0, stream>>>(a, at, M, K, pitch, mask4);
         return launch_status();
     }
     const dim3 block(32, 32), grid((pitch / 16 + 31) / 32, (K + 31) / 32);
