@@ -73,8 +73,9 @@ struct Args {
     const uint16_t *lut;
     uint32_t *c;       // [M,N]
     int M, K, N;
-    int tiles_r, tiles_c, ksplits, k_per_split;
-    int vec_a, vec_w, vec_c;
+    int tiles_r, tiles_c;
+    int share;  // 1: equal shares of (tile, k chunk) pairs per CTA, cut tiles combined with atomics; 0: whole tiles
+    int vec_a, vec_w, vec_c, vec_c4;
     ConvGeom conv;
     const uint8_t *at;  // optional: the activation codes transposed, at[k][m], rows at_pitch bytes apart
     int at_pitch;       // a multiple of 16; columns m >= M hold 0
@@ -218,10 +219,30 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p, const __
         stage_phase ^= 1u << stage;
     };
 
-    const int items = p.tiles_r * p.tiles_c * p.ksplits;
-    for (int item = blockIdx.x; item < items; item += gridDim.x) {
-        const int tile = item / p.ksplits;
-        const int kbeg = (item % p.ksplits) * p.k_per_split, kend = min(K, kbeg + p.k_per_split);
+    // Work items are (tile, k range).  Without a K split: whole tiles, round-robin.  With one (p.share): the
+    // (tile, 16-k chunk) pairs of the whole problem, tile-major, are cut into gridDim.x equal contiguous shares, so all
+    // CTAs finish together; a share covers the tail of one tile's k range, whole tiles and the head of another, and
+    // the sums of a tile that is cut are combined with integer atomics (exact in any order).
+    const long kchunks = (K + KC - 1) / KC;
+    const long total_chunks = (long)p.tiles_r * p.tiles_c * kchunks;
+    long cur = p.share ? total_chunks * blockIdx.x / gridDim.x : (long)blockIdx.x;
+    const long cur_end = p.share ? total_chunks * (blockIdx.x + 1) / gridDim.x : (long)p.tiles_r * p.tiles_c;
+    while (cur < cur_end) {
+        int tile, kbeg, kend;
+        if (p.share) {
+            tile = (int)(cur / kchunks);
+            const int kc0 = (int)(cur - (long)tile * kchunks);
+            const int kc1 = (int)min(kchunks, (long)kc0 + (cur_end - cur));
+            kbeg = kc0 * KC;
+            kend = min(K, kc1 * KC);
+            cur += kc1 - kc0;
+        } else {
+            tile = (int)cur;
+            kbeg = 0;
+            kend = K;
+            cur += gridDim.x;
+        }
+        const bool partial = kbeg != 0 || kend != K;
         const int m0 = (tile / p.tiles_c) * RT, n0 = (tile % p.tiles_c) * CT;
 
         // HW: half a warp per slab row, two words (four columns) per lane: acc[2 * i + w] belongs to row i of the lane's
@@ -316,7 +337,15 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p, const __
                     continue;
                 }
                 uint32_t *crow = p.c + (size_t)m * N;
-                if (p.ksplits > 1) {
+                if (HW && !partial && p.vec_c4) {
+                    // the lane's four columns of this row in one 16-byte store (acc[r] and acc[r + 1] are one row)
+                    if ((r & 1) == 0 && n < N) {
+                        const uint32_t lo1 = acc[r + 1][0] - (acc[r + 1][1] << 16);
+                        *reinterpret_cast<uint4 *>(crow + n) = make_uint4(acc[r][0], acc[r][1], lo1, acc[r + 1][1]);
+                    }
+                    continue;
+                }
+                if (partial) {
                     if (n < N) atomicAdd(crow + n, acc[r][0]);
                     if (n + 1 < N) atomicAdd(crow + n + 1, acc[r][1]);
                 } else if (p.vec_c) {
@@ -381,18 +410,18 @@ static int launch_fwd_slab(const uint8_t *a, const uint8_t *w, uint32_t *c, cons
     p.tiles_r = (M + C::RT - 1) / C::RT;
     p.tiles_c = (N + C::CT - 1) / C::CT;
     const long tiles = (long)p.tiles_r * p.tiles_c;
-    const int kchunks = (K + C::KC - 1) / C::KC;
-    // (with a fused epilogue every tile must hold complete sums: the caller only asks for it when no K split pays)
-    const int ksplits = epi ? 1 : slab_fwd_ksplits(M, K, N, num_sms);
-    p.ksplits = ksplits;
-    p.k_per_split = ((kchunks + ksplits - 1) / ksplits) * C::KC;
-    const long items = tiles * ksplits;
-    const int grid = (int)(items < num_sms ? items : num_sms);
-    if (ksplits > 1 && !cuda_ok(cudaMemsetAsync(c, 0, (size_t)M * N * sizeof(uint32_t), stream)))
+    const long kchunks = (K + C::KC - 1) / C::KC;
+    // K is cut where whole tiles would leave the last wave of the persistent grid badly filled (with a fused epilogue
+    // every tile must hold complete sums: the caller only asks for it when no K split pays)
+    p.share = !epi && slab_fwd_ksplits(M, K, N, num_sms) > 1;
+    const long units = p.share ? tiles * kchunks : tiles;
+    const int grid = (int)(units < num_sms ? units : num_sms);
+    if (p.share && !cuda_ok(cudaMemsetAsync(c, 0, (size_t)M * N * sizeof(uint32_t), stream)))
         return LUTGEMM_E_CUDA;
     p.vec_a = !conv.enabled && (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(a) & 15) == 0);
     p.vec_w = (N % 16 == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
     p.vec_c = (N % 2 == 0) && ((reinterpret_cast<uintptr_t>(c) & 7) == 0);
+    p.vec_c4 = (N % 4 == 0) && ((reinterpret_cast<uintptr_t>(c) & 15) == 0);
     kern<<<grid, C::THREADS, C::SMEM, stream>>>(p, map_at, map_w);
     return launch_status();
 }
