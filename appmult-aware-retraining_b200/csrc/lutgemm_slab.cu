@@ -9,9 +9,9 @@
 //   build (once per k):  U_k[x][n] = LUT[x][w[k,n]]   for every code x and the 64 columns  (gather by w)
 //   use   (per row m):   row a[m,k] of U_k, read contiguously over n and added to the accumulators.
 //
-// The use-phase read is warp-uniform in x and contiguous in n: one 32-bit shared load per lane returns
-// two adjacent uint16 entries (two columns), conflict-free by construction - 64 table look-ups per
-// shared-memory wavefront instead of ~11.  The build reads the table transposed and paired ([w][x],
+// The use-phase read is uniform in x and contiguous in n: half a warp reads one slab row, one 64-bit shared load
+// per lane returns four adjacent uint16 entries (four columns), conflict-free by construction - 64 table
+// look-ups per shared-memory wavefront instead of ~11, and two rows per load instruction.  The build reads the table transposed and paired ([w][x],
 // codes x and x + 2^b/2 in one word) with conflict-free 32-bit loads and writes slab rows (stride 34
 // words) with conflict-free 64-bit stores: 2^b * 2 wavefronts per k against 512 for the use phase.
 // Two slab buffers: slab k+1 is built while slab k is read, one CTA barrier per k.  (Handing the buffers over
@@ -21,8 +21,9 @@
 // the gradients'.)
 // The two halves of a slab word go to the accumulators as  S += word,  H += word >> 16 ; at the end
 // sum(lo) = S - (H << 16) (mod 2^32) and sum(hi) = H.
-// Work items are (tile, K split); splits of one tile are combined with integer atomics, which are
-// exact in any order, so the result stays bit-identical.  The activation codes come either from a
+// Work items are (tile, k range): whole tiles where they fill the persistent grid's waves, otherwise every CTA
+// takes an equal contiguous share of all (tile, 16-k chunk) pairs; the parts of a tile that is cut are combined
+// with integer atomics, which are exact in any order, so the result stays bit-identical.  The activation codes come either from a
 // transposed copy at[k][m] in a workspace (16 rows of one k per 16-byte load, coalesced; for a convolution
 // that copy is the uint8 im2col, made once) or, without a workspace, straight from a[m][k] - with
 // conv.enabled gathered from the NCHW code image on the fly (implicit im2col) - and transposed byte-wise

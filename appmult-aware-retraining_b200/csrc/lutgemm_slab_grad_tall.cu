@@ -6,8 +6,9 @@
 //            rows r = (tap, n), columns = input pixels, the k loop runs over the input channels c
 //
 // Per k a slab U_k[x][c] = T(x, cc[k,c]) is gathered once, then every row reads slab row rc[r,k] contiguously
-// (one fp32 column per lane, conflict-free) and multiplies it with its grad_out entries held in registers
-// (RW per thread).  The 2^b-row build is paid once per 16*RW rows; two slab buffers, so slab k+1 is built
+// (conflict-free: with RW = 64 half a warp per row and two fp32 columns per lane in one 64-bit load, otherwise a
+// warp per row and one column per lane) and multiplies it with its grad_out entries held in registers (RW per
+// thread).  The 2^b-row build is paid once per 16*RW rows; two slab buffers, so slab k+1 is built
 // while slab k is read.
 //
 // grad_x is the activation gradient of a convolution WITHOUT the unfolded intermediate: every tap that
