@@ -36,14 +36,14 @@ __global__ void __launch_bounds__(256) quant_tile_kernel(const float *__restrict
     __shared__ float tile[32][33];
     const float scale = *scale_p, zp = *zp_p;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
-    const int wt = (W + 31) / 32, ct = (C + 31) / 32;
-    const long tiles = (long)B * H * wt * ct;
+    const int ct = (C + 31) / 32;
     const bool chan_fast = sc == 1 && sw != 1;
-    for (long t = blockIdx.x; t < tiles; t += gridDim.x) {
-        const int c0 = (int)(t % ct) * 32;
-        const int w0 = (int)((t / ct) % wt) * 32;
-        const long bh = t / ((long)ct * wt);
-        const int h = (int)(bh % H), b = (int)(bh / H);
+    // one tile per CTA: blockIdx.x = (column tile, channel tile), blockIdx.y = image row, blockIdx.z = image (no
+    // 64-bit divisions to decode a linear tile index: they cost more than the tile's arithmetic)
+    {
+        const int c0 = (int)(blockIdx.x % ct) * 32;
+        const int w0 = (int)(blockIdx.x / ct) * 32;
+        const int h = blockIdx.y, b = blockIdx.z;
         const float *xrow = x + b * sb + h * sh;
         // tile[c][w] = q (forward) or the clamp mask (backward)
 #pragma unroll
@@ -96,7 +96,6 @@ __global__ void __launch_bounds__(256) quant_tile_kernel(const float *__restrict
                 if (c < C && w < W) grow[c * sc + w * sw] = chan_fast ? tile[tx][i] : tile[i][tx];
             }
         }
-        __syncthreads();
     }
 }
 
@@ -107,18 +106,25 @@ __global__ void __launch_bounds__(256) conv_epilogue_kernel(const uint32_t *__re
                                                             const float *__restrict__ bias, float *__restrict__ out, long M,
                                                             int L, int Cout) {
     const float s = *sa_p * *sw_p, za = *za_p, zw = *zw_p, zz = za * zw;
-    const long total = M * Cout;
-    for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
-        const long m = idx / Cout;
-        const int co = (int)(idx - m * Cout), l = (int)(m % L);
+    // a warp per output row m (32 rows per CTA per step), lanes over the output channels: the row terms and the
+    // position l = m mod L are computed once per row, and nothing divides by Cout per element
+    const int lane = threadIdx.x & 31, wrow = threadIdx.x >> 5;
+    for (long m = (long)blockIdx.x * 8 + wrow; m < M; m += (long)gridDim.x * 8) {
+        const int l = (int)(m % L);
         // separately rounded products and sums, in the order the PyTorch expression evaluates them
-        float acc = (float)y[idx];
-        acc = __fadd_rn(acc, __fmul_rn(zw, box[m]));
-        acc = __fadd_rn(acc, __fmul_rn(za, sumw_t[(size_t)l * Cout + co]));
-        acc = __fadd_rn(acc, __fmul_rn(zz, taps[l]));
-        float o = __fmul_rn(s, acc);
-        if (bias) o = __fadd_rn(o, bias[co]);
-        out[idx] = o;
+        const float zw_box = __fmul_rn(zw, box[m]), zz_taps = __fmul_rn(zz, taps[l]);
+        const uint32_t *yrow = y + m * Cout;
+        const float *srow = sumw_t + (size_t)l * Cout;
+        float *orow = out + m * Cout;
+        for (int co = lane; co < Cout; co += 32) {
+            float acc = (float)yrow[co];
+            acc = __fadd_rn(acc, zw_box);
+            acc = __fadd_rn(acc, __fmul_rn(za, srow[co]));
+            acc = __fadd_rn(acc, zz_taps);
+            float o = __fmul_rn(s, acc);
+            if (bias) o = __fadd_rn(o, bias[co]);
+            orow[co] = o;
+        }
     }
 }
 
@@ -126,8 +132,9 @@ __global__ void __launch_bounds__(256) conv_epilogue_kernel(const uint32_t *__re
 
 int quantize_codes(const float *x, long sb, long sc, long sh, long sw, int B, int C, int H, int W, const float *scale,
                    const float *zp_neg, float qmax, uint8_t *codes, float *chansum, int num_sms, cudaStream_t stream) {
-    const long tiles = (long)B * H * ((W + 31) / 32) * ((C + 31) / 32);
-    const int grid = (int)(tiles < 16L * num_sms ? tiles : 16L * num_sms);
+    (void)num_sms;
+    if (H > 65535 || B > 65535) return LUTGEMM_E_TOOLARGE;
+    const dim3 grid((unsigned)(((W + 31) / 32) * ((C + 31) / 32)), (unsigned)H, (unsigned)B);
     quant_tile_kernel<false><<<grid, 256, 0, stream>>>(x, sb, sc, sh, sw, B, C, H, W, scale, zp_neg, qmax, codes, chansum,
                                                        nullptr, nullptr, nullptr, nullptr, nullptr);
     return launch_status();
@@ -136,8 +143,9 @@ int quantize_codes(const float *x, long sb, long sc, long sh, long sw, int B, in
 int quantize_backward(const float *x, long sb, long sc, long sh, long sw, int B, int C, int H, int W, const float *scale,
                       const float *zp_neg, float qmax, const float *gcodes, const float *boxT, const float *s_w,
                       const float *z_w, float *gx, int num_sms, cudaStream_t stream) {
-    const long tiles = (long)B * H * ((W + 31) / 32) * ((C + 31) / 32);
-    const int grid = (int)(tiles < 16L * num_sms ? tiles : 16L * num_sms);
+    (void)num_sms;
+    if (H > 65535 || B > 65535) return LUTGEMM_E_TOOLARGE;
+    const dim3 grid((unsigned)(((W + 31) / 32) * ((C + 31) / 32)), (unsigned)H, (unsigned)B);
     quant_tile_kernel<true><<<grid, 256, 0, stream>>>(x, sb, sc, sh, sw, B, C, H, W, scale, zp_neg, qmax, nullptr, nullptr,
                                                       gcodes, boxT, s_w, z_w, gx);
     return launch_status();
@@ -146,7 +154,7 @@ int quantize_backward(const float *x, long sb, long sc, long sh, long sw, int B,
 int conv_epilogue(const uint32_t *y, const float *box, const float *sumw_t, const float *taps, const float *s_a,
                   const float *s_w, const float *z_a, const float *z_w, const float *bias, float *out, long M, int L,
                   int Cout, int num_sms, cudaStream_t stream) {
-    const long blocks = (M * Cout + 255) / 256;
+    const long blocks = (M + 7) / 8;
     const int grid = (int)(blocks < 32L * num_sms ? blocks : 32L * num_sms);
     conv_epilogue_kernel<<<grid, 256, 0, stream>>>(y, box, sumw_t, taps, s_a, s_w, z_a, z_w, bias, out, M, L, Cout);
     return launch_status();
