@@ -121,6 +121,7 @@ __global__ void __launch_bounds__(512, 1) slab_fwd_kernel(const Args p, const __
     // ---- stage the table transposed and paired: tt[w][i] = { LUT[i][w], LUT[i + HALF][w] } ---------------
     {
         uint16_t *tt16 = reinterpret_cast<uint16_t *>(smem);
+#pragma unroll 8
         for (int idx = tid; idx < Q * Q; idx += THREADS) {
             const int x = idx >> BITS, y = idx & (Q - 1);  // global read contiguous in y
             tt16[(y * TTS + (x & (HALF - 1))) * 2 + (x >> (BITS - 1))] = p.lut[x * COL + y];

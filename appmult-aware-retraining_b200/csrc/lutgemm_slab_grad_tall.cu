@@ -128,6 +128,7 @@ __global__ void __launch_bounds__(512, 1) slab_grad_tall_kernel(const Args p) {
 
     // ---- stage the gradient table; x = row code, y = column code, T(x,y) = lut[a*COL + w] ----------------
     // (grad_w: rows are activation codes; grad_a / grad_x: rows are weight codes)
+#pragma unroll 8
     for (int idx = tid; idx < Q * Q; idx += THREADS) {
         const int hi_idx = idx >> BITS, lo_idx = idx & (Q - 1);  // global read contiguous in lo_idx
         const int x = MODE == kGw ? hi_idx : lo_idx, y = MODE == kGw ? lo_idx : hi_idx;
