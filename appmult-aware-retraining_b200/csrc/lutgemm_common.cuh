@@ -185,15 +185,18 @@ __device__ __forceinline__ void stage_table(T *dst, const T *__restrict__ src, i
             // rows start at a*COL (COL even) so pairs of entries are 4-byte aligned
             const uint32_t *s32 = reinterpret_cast<const uint32_t *>(src);
             uint32_t *d32 = reinterpret_cast<uint32_t *>(dst);
+#pragma unroll 8
             for (int i = tid; i < Q * Q / 2; i += nthreads) {
                 int a = i / (Q / 2), wp = i % (Q / 2);
                 d32[i] = __ldg(s32 + a * (COL / 2) + wp);
             }
         } else {
+#pragma unroll 8
             for (int i = tid; i < Q * Q; i += nthreads) dst[i] = src[(i >> BITS) * COL + (i & (Q - 1))];
         }
     } else {
         // consecutive threads take consecutive a (contiguous shared-memory writes, strided L2 reads)
+#pragma unroll 8
         for (int i = tid; i < Q * Q; i += nthreads) {
             int w = i >> BITS, a = i & (Q - 1);
             dst[i] = src[a * COL + w];

@@ -92,6 +92,7 @@ __global__ void __launch_bounds__(32 * WARPS, 1) slab_grad_kernel(const Args p) 
     const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
 
     // ---- stage the gradient table; x = row code, y = column code, T(x,y) = lut[a*COL + w] ----------------
+#pragma unroll 8
     for (int idx = tid; idx < Q * Q; idx += THREADS) {
         const int hi_idx = idx >> BITS, lo_idx = idx & (Q - 1);  // global read contiguous in lo_idx
         const int16_t v = p.lut[hi_idx * COL + lo_idx];
