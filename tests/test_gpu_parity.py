@@ -133,6 +133,17 @@ def test_each_backward_kernel_on_every_shape_class(dev, oracle_c, bits, kernel, 
         check_backward(oracle_c, gc, a, w, la, lw, bits, ga, gw)
 
 
+@pytest.mark.parametrize("bits", [6, 8])
+def test_forward_tiles_cut_across_ctas(dev, oracle_c, bits):
+    """Few tiles and a long K: the forward slab kernel gives every CTA an equal share of the (tile, k chunk) pairs, so
+    each tile is cut many times and its parts are combined with integer atomics - the sums must stay bit-exact, with
+    and without 16-byte aligned output rows, and whole tiles (16-byte stores) next to cut ones."""
+    lf, _, _ = synth_wire(bits, seed=40 + bits)
+    for s, (M, K, N) in enumerate([(1100, 4096, 200), (512, 8192, 64), (3000, 1040, 130), (9000, 528, 128)]):
+        a, w, _ = rand_problem(bits, M, K, N, seed=13 * bits + s)
+        assert np.array_equal(run_forward(dev, a, w, lf), oracle_c.forward(a, w, lf, bits)), (bits, M, K, N)
+
+
 @pytest.mark.parametrize("bits", [7, 8])
 def test_extreme_codes(dev, oracle_c, bits):
     lf, la, lw = synth_wire(bits, seed=3)
