@@ -219,14 +219,17 @@ ga_colbcast_kernel(const float *__restrict__ gc, const uint8_t *__restrict__ a, 
                 uint32_t w4[R];
                 float4 g4[C];
 #pragma unroll
-                for (int i = 0; i < R; ++i) w4[i] = *reinterpret_cast<const uint32_t *>(ws + i * NT + n4);
+                for (int i = 0; i < R; ++i) w4[i] = *reinterpret_cast<const uint32_t *>(ws + i * NT + n4) & MASK4;
 #pragma unroll
                 for (int j = 0; j < C; ++j) g4[j] = *reinterpret_cast<const float4 *>(gs + (32 * j) * GS + n4 * 4);
 #pragma unroll
                 for (int nn = 0; nn < 4; ++nn) {
 #pragma unroll
                     for (int i = 0; i < R; ++i) {
-                        const uint32_t wrow = lut_addr + ((byte_of(w4[i], nn) & MASK) << (BITS + 1));
+                        // table row of the weight code (already cut to BITS bits): at 7 bits a row is 256 bytes, so one
+                        // byte permutation puts the code where the row offset needs it
+                        const uint32_t wrow = BITS == 7 ? lut_addr + __byte_perm(w4[i], 0u, 0x4404u | (nn << 4))
+                                                        : lut_addr + (byte_of(w4[i], nn) << (BITS + 1));
 #pragma unroll
                         for (int j = 0; j < C; ++j) {
                             const float g = nn == 0 ? g4[j].x : nn == 1 ? g4[j].y : nn == 2 ? g4[j].z : g4[j].w;
