@@ -22,8 +22,8 @@ namespace lutgemm {
 
 namespace {
 
-__device__ __forceinline__ float code_of(float x, float scale, float zp_neg) {
-    return rintf(__fsub_rn(__fdiv_rn(x, scale), zp_neg));  // two roundings, as x / scale - zp in PyTorch
+__device__ __forceinline__ float code_of(float x, const Divisor &scale, float zp_neg) {
+    return rintf(__fsub_rn(quotient(x, scale), zp_neg));  // two roundings, as x / scale - zp in PyTorch
 }
 
 // one thread: the layer's observers and quantisation parameters
@@ -58,7 +58,8 @@ __global__ void __launch_bounds__(256) weight_prep_kernel(const float *__restric
                                                           uint8_t *__restrict__ wmat, float *__restrict__ wsum) {
     extern __shared__ float tap_sum[];  // [kh*kw]
     const int T = kh * kw, K = Cin * T, co = blockIdx.x;
-    const float scale = quant[2], zp = quant[3];
+    const Divisor scale = make_divisor(quant[2]);
+    const float zp = quant[3];
     for (int t = threadIdx.x; t < T; t += blockDim.x) tap_sum[t] = 0.f;
     __syncthreads();
     for (int k = threadIdx.x; k < K; k += blockDim.x) {
@@ -146,7 +147,8 @@ __global__ void __launch_bounds__(256) weight_grad_finish_kernel(const float *__
                                                                  const float *__restrict__ quant, float qmax,
                                                                  float *__restrict__ gw) {
     const int T = kh * kw, K = Cin * T;
-    const float s_a = quant[0], z_a = quant[1], scale = quant[2], zp = quant[3];
+    const float s_a = quant[0], z_a = quant[1], zp = quant[3];
+    const Divisor scale = make_divisor(quant[2]);
     for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < (long)K * Cout; idx += (long)gridDim.x * blockDim.x) {
         const int k = (int)(idx / Cout), co = (int)(idx - (long)k * Cout);  // gwmat is read in its own order
         const int c = k / T, t = k - c * T, i = t / kw, j = t - i * kw;

@@ -19,8 +19,8 @@ namespace lutgemm {
 
 namespace {
 
-__device__ __forceinline__ float code_of(float x, float scale, float zp_neg) {
-    return rintf(__fsub_rn(__fdiv_rn(x, scale), zp_neg));  // two roundings, as x / scale - zp in PyTorch
+__device__ __forceinline__ float code_of(float x, const Divisor &scale, float zp_neg) {
+    return rintf(__fsub_rn(quotient(x, scale), zp_neg));  // two roundings, as x / scale - zp in PyTorch
 }
 
 // Tile of 32 channels x 32 columns of one image row (b, h).  Reads follow the input's fastest dimension,
@@ -34,7 +34,8 @@ __global__ void __launch_bounds__(256) quant_tile_kernel(const float *__restrict
                                                          const float *__restrict__ sw_p, const float *__restrict__ zw_p,
                                                          float *__restrict__ gx) {
     __shared__ float tile[32][33];
-    const float scale = *scale_p, zp = *zp_p;
+    const Divisor scale = make_divisor(*scale_p);
+    const float zp = *zp_p;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
     const int ct = (C + 31) / 32;
     const bool chan_fast = sc == 1 && sw != 1;
