@@ -93,3 +93,29 @@ def test_window_sums(dev):
         lhs = float((approx_ops.layer_window_sum(u, kh, kw, st, p, d).double() * g.reshape(-1).double()).sum())
         rhs = float((u.double() * adj.double()).sum())
         assert abs(lhs - rhs) <= 1e-5 * max(abs(lhs), 1.0)
+
+
+def test_quantisation_division_matches_ieee_division_for_awkward_scales(dev):
+    """The quantisation kernels divide by the common scale with a reciprocal and one fused correction; the codes must
+    equal clamp(round(x / scale - zp)) evaluated with PyTorch's IEEE division for scales whose mantissa is all ones,
+    a power of two, or random, and for activations that are zero, tiny, huge or infinite."""
+    import approx_ops
+    g = torch.Generator(device=dev).manual_seed(5)
+    x = torch.randn(4, 40, 9, 33, device=dev, generator=g) * 3.0
+    flat = x.view(-1)
+    flat[::97] = 0.0
+    flat[1::193] = 1e-38
+    flat[2::211] = -3e37
+    flat[3::389] = float("inf")
+    flat[4::401] = -float("inf")
+    x = x.contiguous(memory_format=torch.channels_last)
+    mant = [0x7FFFFF, 0x7FFFFE, 0x000000, 0x000001, 0x400000, 0x2AAAAB, 0x555555, 0x123457]
+    for bits, qmax in ((7, 127.0), (8, 255.0)):
+        for i, m in enumerate(mant):
+            for e in (110, 121, 127, 130):
+                scale = torch.tensor([(e << 23) | m], dtype=torch.int32, device=dev).view(torch.float32)
+                zp = torch.tensor([float(-(17 + 9 * i) % int(qmax))], device=dev).neg()
+                codes, _ = approx_ops.quantize_activations(x, scale, zp, qmax, want_chansum=False)
+                want = torch.clamp(torch.round(x / scale - zp), 0.0, qmax)
+                want = torch.nan_to_num(want, nan=0.0).to(torch.uint8)
+                assert torch.equal(codes, want.contiguous()), (bits, hex(m), e)
